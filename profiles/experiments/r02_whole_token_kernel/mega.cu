@@ -5,7 +5,7 @@
 // time (profiles/r02_*: Qwen2.5-0.5B 0.37 of the HBM roofline), and for the large ones HBM idles across every
 // boundary.  Here 148 CTAs (one per SM) stay resident for the whole token:
 //   * warp 8 of every CTA is a TMA producer that streams THIS CTA's share of every weight matrix of the token, in op
-//     order, through one shared-memory ring (cp.async.bulk.tensor.2d → SASS UTMALDG, full/empty mbarriers).  It never
+//     order, through one shared-memory ring (cp.async.bulk.tensor.2d, full/empty mbarriers).  It never
 //     waits for an activation, so HBM keeps streaming across op, layer and token boundaries; the ring (≈ 190 KB per
 //     SM, 28 MB chip-wide) is what decouples it from the consumers.
 //   * warps 0–7 consume: for every op they wait for the activation vector, run the (fused) prologue, dot their rows

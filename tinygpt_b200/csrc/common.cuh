@@ -162,7 +162,7 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
-// ---- TMA: 2-D tiled bulk tensor load global → shared, completion on an mbarrier (SASS: UTMALDG)
+// ---- TMA: 2-D tiled bulk tensor load global → shared, completion on an mbarrier
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t c0, int32_t c1,
                                             uint64_t* bar) {
   asm volatile(

@@ -10,7 +10,7 @@
 //
 // Design (HBM-bound: 2 bytes of W per FMA, so the only goal is to keep HBM saturated):
 //   * W[n,k] row-major is cut into boxes of (8·RPW rows) × (256 columns) = RPW·4 KB.  One elected producer thread
-//     streams the boxes of this CTA's row blocks with TMA (cp.async.bulk.tensor.2d → SASS UTMALDG) into a ring of
+//     streams the boxes of this CTA's row blocks with TMA (cp.async.bulk.tensor.2d) into a ring of
 //     `stages` shared-memory slots guarded by full/empty mbarriers; no registers are spent on loads in flight and
 //     ~80 KB per SM stay outstanding.
 //   * 8 consumer warps: warp w owns rows w·RPW … w·RPW+RPW-1 of the box; a lane reads one 16-byte vector of x and
