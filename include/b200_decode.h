@@ -30,8 +30,10 @@ extern "C" {
 #endif
 
 /* 2: + b200_engine_set_mailbox, b200_engine_generated;  3: + b200_sample_bf16, b200_sample_workspace_bytes,
- * b200_engine_set_sampler, b200_engine_options.  All additive: callers of an older version keep working. */
-#define B200_ABI_VERSION 3
+ * b200_engine_set_sampler, b200_engine_options;  4: + layer-stack models (b200_stack_desc, b200_engine_create_stack),
+ * sequence slots and the ragged step (b200_engine_step, b200_engine_slot_*), the per-mechanism stack ops.  All additive:
+ * callers of an older version keep working. */
+#define B200_ABI_VERSION 4
 
 typedef enum b200_status {
   B200_OK = 0,
@@ -270,6 +272,117 @@ int64_t b200_engine_launches_per_token(const b200_engine* eng);
 int64_t b200_engine_options(const b200_engine* eng);
 /* Algorithmic HBM bytes one decode step reads on THIS rank at context length ctx (weights once + KV + logits). */
 int64_t b200_engine_bytes_per_token(const b200_engine* eng, int64_t ctx);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Layer-stack models: a model described as DATA — a list of layer runs, each with a mixer, an optional gated
+ * feed-forward and an optional per-token side input — instead of the fixed Llama-family wiring above.  The same engine
+ * handle, entry points (forward / decode / reset / seek / last_token / set_sampler), argmax and sampler kernels serve
+ * it.  What a stack engine adds to the engine:
+ *   - the residual stream, every norm, the softmax and the gates are fp32; matrix products take bf16 operands with
+ *     fp32 accumulation (B200_BF16) or are true fp32 FMA chains (B200_F32: weights, caches and activations in fp32);
+ *   - sequence SLOTS: `max_slots` independent KV caches of `max_ctx` rows with their own positions, and a RAGGED step
+ *     (b200_engine_step) that runs any number of new tokens for any subset of the slots in one pass;
+ *   - attention with arbitrary head sizes (key size ≠ value size), an explicit score scale, a sliding window with kept
+ *     first keys, and a per-head sigmoid output gate; gated feed-forward with tanh-GELU; a parallel block
+ *     (x += m·(mixer(h) + ff(h)), one norm); a looped span of layers (own cache per pass) whose passes start with a
+ *     projection of [x; x0]; a gated per-layer token table added through a weighted RMS norm.
+ * Weight layout (built by tinygpt_b200/loader.py): the projections that read the block norm are merged by rows into
+ * w_in = [q | k | v | gate logits | ff gate | ff up] (segments padded to 8 rows), the projections that feed the
+ * residual are merged by columns into w_out = [o | ff down]; vectors (norm weights, biases) are fp32.
+ * ---------------------------------------------------------------------------------------------------------------- */
+typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1 } b200_dtype;
+typedef enum b200_block_kind { B200_BLOCK_PARALLEL = 0 } b200_block_kind;
+typedef enum b200_ff_act { B200_ACT_GELU_TANH = 0, B200_ACT_SILU = 1 } b200_ff_act;
+
+typedef struct b200_attn_desc {
+  int32_t heads;       /* query heads */
+  int32_t kv_heads;    /* key/value heads; query head h reads kv head h / (heads / kv_heads) */
+  int32_t dim;         /* per-head query/key size */
+  int32_t vdim;        /* per-head value size */
+  float scale;         /* score = (q·k)·scale */
+  int32_t window;      /* key j visible from query i when j <= i and i - j < window; 0 = every earlier key */
+  int32_t keep_first;  /* keys j < keep_first stay visible whatever the window */
+  int32_t out_gate;    /* 1: head output × sigmoid(gate logit of that head) */
+} b200_attn_desc;
+
+typedef struct b200_stack_layer {
+  b200_attn_desc attn;
+  int32_t ff;          /* feed-forward width; 0 = the layer has none */
+  int32_t ff_act;      /* b200_ff_act */
+  int32_t off_q, off_k, off_v, off_g, off_gate, off_up, n_in; /* first row of each segment of w_in; n_in = all rows */
+  int32_t off_act, k_out; /* w_out columns: [0, heads·vdim) attention, [off_act, off_act + ff) feed-forward; k_out = all */
+  const float* norm;   /* [width] */
+  const void* w_in;    /* [n_in, width] */
+  const float* b_in;   /* [n_in] (0 where a segment has no bias) or NULL */
+  const void* w_out;   /* [width, k_out] */
+  int32_t side_col;    /* first column of this layer's part of the side table */
+  const void* side_gate; /* [side_dim, width] or NULL: no side input */
+  const void* side_proj; /* [width, side_dim] */
+  const float* side_norm; /* [width] */
+} b200_stack_layer;
+
+typedef struct b200_stack_desc {
+  int32_t dtype;         /* b200_dtype of matrices, caches and activations */
+  int32_t block;         /* b200_block_kind */
+  int32_t width, vocab, n_layers, n_runs;
+  const int32_t* run_layer_host;  /* [n_runs] which layer each run executes (a looped layer appears once per pass) */
+  const int32_t* run_mix_host;    /* [n_runs] 1: before this run x <- mix_in·[x; x0] (x0 = the embedding output) */
+  float embed_scale, residual_mult, norm_eps;
+  float norm_offset;     /* block and final norms multiply by (norm_offset + w) */
+  int32_t side_dim, side_stride;  /* columns per layer / per row of side_table */
+  int32_t max_ctx, max_slots;
+  const void* embed;     /* [vocab, width] */
+  const void* mix_in;    /* [width, 2·width] or NULL */
+  const void* side_table; /* [vocab, side_stride] or NULL */
+  const float* final_norm; /* [width] */
+  const void* head;      /* [vocab, width] */
+  const b200_stack_layer* layers_host;
+} b200_stack_desc;
+
+/* Build a stack engine (single GPU).  Borrows the weights; owns the caches [slot][run][max_ctx][kv_heads·dim | ·vdim],
+ * the per-slot positions / current tokens / token logs and a workspace that grows with the largest step. */
+int b200_engine_create_stack(const b200_stack_desc* desc, b200_engine** out);
+
+/* Ragged step: sequence i (slot slots_host[i]) consumes counts_host[i] new tokens, taken in order from ids_host; every
+ * token attends to its slot's cache and to the earlier tokens of its own sequence in this step.  want_host lists flat
+ * indices into ids_host whose logits are written, in that order, to logits_out_dev (fp32 [n_want, vocab], device).
+ * greedy != 0: the argmax (or the configured sampler) of the LAST token of every sequence becomes that slot's current
+ * token, so b200_engine_decode can go on, and the sequences become the engine's active batch.
+ * The logits at a position depend neither on how its prompt was cut into steps nor on the other sequences of a step.
+ * Host arrays may be freed on return. */
+int b200_engine_step(b200_engine* eng, int64_t n_seq, const int32_t* slots_host, const int32_t* counts_host,
+                     const int64_t* ids_host, int64_t n_want, const int32_t* want_host, float* logits_out_dev,
+                     int greedy, void* stream);
+/* Give a slot back: its position returns to 0 and its cache rows are overwritten by the next sequence. */
+int b200_engine_slot_reset(b200_engine* eng, int64_t slot, void* stream);
+int64_t b200_engine_slot_position(const b200_engine* eng, int64_t slot);
+int64_t b200_engine_max_slots(const b200_engine* eng);
+
+/* The stack engine's mechanisms as stand-alone ops (dtype = b200_dtype of T; fp32 where the name says so), exported so
+ * that parity tests drive the kernels the engine runs. */
+/* y[r,:] = T( x[r,:] · rsqrt(mean(x[r,:]²) + eps) · (offset + w[:]) ), x fp32 */
+int b200_stack_rmsnorm(void* y, const float* x, const float* w, int64_t rows, int64_t dim, float eps, float offset,
+                       int dtype, void* stream);
+/* C[M,N] = A[M,K]·W[N,K]ᵀ (+ bias[N]) with fp32 accumulation; A, W, C of dtype T (any M, N, K) */
+int b200_stack_linear(void* C, const void* A, const void* W, const float* bias_or_null, int64_t M, int64_t N, int64_t K,
+                      int dtype, void* stream);
+/* Attention of n_tok new tokens over per-slot caches: token t (slot[t], position pos[t]) reads its q (and gate logit)
+ * from `proj` (row stride ld_proj, segments at off_q / off_g) and the keys of its slot's cache
+ * kcache[slot·k_slot_stride + j·kv_heads·dim …], j visible under (window, keep_first); out[t, h·vdim …] (row stride
+ * ld_out).  The rows of this step's own tokens must already be in the cache (b200_stack_kv_store). */
+int b200_stack_attention(void* out, int64_t ld_out, const void* proj, int64_t ld_proj, int64_t off_q, int64_t off_g,
+                         const void* kcache, const void* vcache, int64_t k_slot_stride, int64_t v_slot_stride,
+                         const int32_t* slot, const int32_t* pos, int64_t n_tok, const b200_attn_desc* attn, int dtype,
+                         void* stream);
+int b200_stack_kv_store(void* kcache, void* vcache, int64_t k_slot_stride, int64_t v_slot_stride, const void* proj,
+                        int64_t ld_proj, int64_t off_k, int64_t off_v, const int32_t* slot, const int32_t* pos,
+                        int64_t n_tok, const b200_attn_desc* attn, int dtype, void* stream);
+/* y[r, j] = T( act(g[r, j]) · u[r, j] ) over row-strided operands */
+int b200_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, int64_t ld_gu, int64_t rows, int64_t n,
+                       int act, int dtype, void* stream);
+/* x[r,:] += mult · y[r,:] · rsqrt(mean(y[r,:]²) + eps) · w[:]   (all fp32) */
+int b200_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int64_t dim, float eps, float mult,
+                       void* stream);
 
 /* ---- tensor parallel (one process per GPU; the caller exchanges the handles with torch.distributed) ---------- */
 

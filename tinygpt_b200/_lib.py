@@ -35,6 +35,31 @@ class WeightTable(C.Structure):
                 ("rope_table", C.c_void_p), ("layers_host", C.POINTER(LayerWeights))]
 
 
+class AttnDesc(C.Structure):
+    _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
+                ("scale", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("out_gate", C.c_int32)]
+
+
+class StackLayer(C.Structure):
+    _fields_ = [("attn", AttnDesc), ("ff", C.c_int32), ("ff_act", C.c_int32),
+                ("off_q", C.c_int32), ("off_k", C.c_int32), ("off_v", C.c_int32), ("off_g", C.c_int32),
+                ("off_gate", C.c_int32), ("off_up", C.c_int32), ("n_in", C.c_int32),
+                ("off_act", C.c_int32), ("k_out", C.c_int32),
+                ("norm", C.c_void_p), ("w_in", C.c_void_p), ("b_in", C.c_void_p), ("w_out", C.c_void_p),
+                ("side_col", C.c_int32), ("side_gate", C.c_void_p), ("side_proj", C.c_void_p), ("side_norm", C.c_void_p)]
+
+
+class StackDesc(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("block", C.c_int32), ("width", C.c_int32), ("vocab", C.c_int32),
+                ("n_layers", C.c_int32), ("n_runs", C.c_int32),
+                ("run_layer_host", C.POINTER(C.c_int32)), ("run_mix_host", C.POINTER(C.c_int32)),
+                ("embed_scale", C.c_float), ("residual_mult", C.c_float), ("norm_eps", C.c_float),
+                ("norm_offset", C.c_float), ("side_dim", C.c_int32), ("side_stride", C.c_int32),
+                ("max_ctx", C.c_int32), ("max_slots", C.c_int32),
+                ("embed", C.c_void_p), ("mix_in", C.c_void_p), ("side_table", C.c_void_p), ("final_norm", C.c_void_p),
+                ("head", C.c_void_p), ("layers_host", C.POINTER(StackLayer))]
+
+
 # name -> (restype, argtypes); every symbol include/b200_decode.h declares (tests/test_abi.py checks the two agree)
 P, I64, I32, F = C.c_void_p, C.c_int64, C.c_int, C.c_float
 PROTOTYPES = {
@@ -73,6 +98,18 @@ PROTOTYPES = {
     "b200_engine_launches_per_token": (I64, [P]),
     "b200_engine_options": (I64, [P]),
     "b200_engine_bytes_per_token": (I64, [P, I64]),
+    "b200_engine_create_stack": (I32, [C.POINTER(StackDesc), C.POINTER(P)]),
+    "b200_engine_step": (I32, [P, I64, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int64), I64,
+                               C.POINTER(C.c_int32), P, I32, P]),
+    "b200_engine_slot_reset": (I32, [P, I64, P]),
+    "b200_engine_slot_position": (I64, [P, I64]),
+    "b200_engine_max_slots": (I64, [P]),
+    "b200_stack_rmsnorm": (I32, [P, P, P, I64, I64, F, F, I32, P]),
+    "b200_stack_linear": (I32, [P, P, P, P, I64, I64, I64, I32, P]),
+    "b200_stack_attention": (I32, [P, I64, P, I64, I64, I64, P, P, I64, I64, P, P, I64, C.POINTER(AttnDesc), I32, P]),
+    "b200_stack_kv_store": (I32, [P, P, I64, I64, P, I64, I64, I64, P, P, I64, C.POINTER(AttnDesc), I32, P]),
+    "b200_stack_act_mul": (I32, [P, I64, P, P, I64, I64, I64, I32, I32, P]),
+    "b200_stack_rms_add": (I32, [P, P, P, I64, I64, F, F, P]),
     "b200_tp_window_bytes": (I64, [C.POINTER(ModelDesc)]),
     "b200_tp_window_create": (I32, [I64, C.POINTER(P), C.c_char_p]),
     "b200_tp_window_open": (I32, [C.c_char_p, C.POINTER(P)]),

@@ -1,6 +1,7 @@
 // api.cu — C-ABI entry points for the GEMV and the fused building blocks (declared in include/b200_decode.h).
 #include "gemv.cuh"
 #include "ops.cuh"
+#include "stack.cuh"
 
 namespace b200 {
 
@@ -101,6 +102,84 @@ int b200_attn_decode_bf16(void* out, const void* qkv, const void* q_norm, const 
   a.nsplit = attn_decode_nsplit((int)hd, (int)max_ctx);
   a.max_ctx = (int)max_ctx;
   return launch_attn_decode(a, (int)hd, (cudaStream_t)stream, false);
+}
+
+}  // extern "C"
+
+// ---- the stack engine's mechanisms as stand-alone ops
+extern "C" {
+
+int b200_stack_rmsnorm(void* y, const float* x, const float* w, int64_t rows, int64_t dim, float eps, float offset,
+                       int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(dim > 0 && dim < (1ll << 31) && rows < (1ll << 31), "stack_rmsnorm: size out of range");
+  return b200::launch_stack_rmsnorm(y, x, w, nullptr, rows, (int)dim, eps, offset, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_linear(void* C, const void* A, const void* W, const float* bias, int64_t M, int64_t N, int64_t K, int dtype,
+                      void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(M > 0 && N > 0 && K > 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31),
+                 "stack_linear: size out of range");
+  b200::StackGemm g;
+  g.a = A; g.lda = K; g.k1 = (int)K;
+  g.w = W; g.bias = bias; g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.epi = b200::SEPI_STORE; g.c = C; g.ldc = N;
+  return b200::launch_stack_gemm(g, dtype, (cudaStream_t)stream);
+}
+
+static b200::StackAttn stack_attn_args(const void* proj, int64_t ld_proj, const void* kcache, const void* vcache,
+                                       int64_t k_slot_stride, int64_t v_slot_stride, const int32_t* slot,
+                                       const int32_t* pos, int64_t n_tok, const b200_attn_desc* attn) {
+  b200::StackAttn p;
+  if (attn) p.a = *attn;
+  p.proj = proj; p.ld_proj = ld_proj;
+  p.kcache = const_cast<void*>(kcache); p.vcache = const_cast<void*>(vcache);
+  p.k_slot_stride = k_slot_stride; p.v_slot_stride = v_slot_stride;
+  p.slot = slot; p.pos = pos; p.n_tok = (int)n_tok;
+  return p;
+}
+
+int b200_stack_attention(void* out, int64_t ld_out, const void* proj, int64_t ld_proj, int64_t off_q, int64_t off_g,
+                         const void* kcache, const void* vcache, int64_t k_slot_stride, int64_t v_slot_stride,
+                         const int32_t* slot, const int32_t* pos, int64_t n_tok, const b200_attn_desc* attn, int dtype,
+                         void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(attn && n_tok > 0 && n_tok < (1ll << 31), "stack_attention: bad arguments");
+  b200::StackAttn p = stack_attn_args(proj, ld_proj, kcache, vcache, k_slot_stride, v_slot_stride, slot, pos, n_tok, attn);
+  p.off_q = (int)off_q; p.off_g = (int)off_g;
+  p.out = out; p.ld_out = ld_out;
+  return b200::launch_stack_attention(p, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_kv_store(void* kcache, void* vcache, int64_t k_slot_stride, int64_t v_slot_stride, const void* proj,
+                        int64_t ld_proj, int64_t off_k, int64_t off_v, const int32_t* slot, const int32_t* pos,
+                        int64_t n_tok, const b200_attn_desc* attn, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(attn && n_tok > 0 && n_tok < (1ll << 31), "stack_kv_store: bad arguments");
+  b200::StackAttn p = stack_attn_args(proj, ld_proj, kcache, vcache, k_slot_stride, v_slot_stride, slot, pos, n_tok, attn);
+  p.off_k = (int)off_k; p.off_v = (int)off_v;
+  return b200::launch_stack_kv_store(p, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, int64_t ld_gu, int64_t rows, int64_t n, int act,
+                       int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(n > 0 && n < (1ll << 31), "stack_act_mul: size out of range");
+  return b200::launch_stack_act_mul(y, ld_y, g, u, ld_gu, rows, (int)n, act, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int64_t dim, float eps, float mult,
+                       void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(dim > 0 && dim < (1ll << 31) && rows < (1ll << 31), "stack_rms_add: size out of range");
+  return b200::launch_stack_rms_add(x, y, w, rows, (int)dim, eps, mult, (cudaStream_t)stream);
 }
 
 }  // extern "C"

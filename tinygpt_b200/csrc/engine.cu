@@ -19,94 +19,10 @@
 #include <new>
 #include <vector>
 
-#include "gemv.cuh"
-#include "ops.cuh"
-
-struct b200_engine {
-  b200_model_desc d{};
-  int num_sms = 148;
-  int qdim = 0, kvdim = 0, Hq_l = 0, Hkv_l = 0, I_l = 0, V_l = 0;  // local (per-rank) sizes
-  // borrowed weights
-  const __nv_bfloat16* embed = nullptr;
-  const float* rope = nullptr;
-  std::vector<b200_layer_weights> lw;
-  // owned device memory
-  uint8_t* arena = nullptr;
-  size_t arena_bytes = 0;
-  __nv_bfloat16 *kcache = nullptr, *vcache = nullptr;  // [L][max_ctx][Hkv_l][hd] each
-  __nv_bfloat16 *x = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *logits = nullptr;
-  float* attn_ws = nullptr;
-  unsigned int* attn_tickets = nullptr;
-  void* argmax_ws = nullptr;
-  int64_t* cur_tok = nullptr;   // token the next step consumes
-  int64_t* gen_log = nullptr;   // ring of generated tokens
-  int* pos = nullptr;           // position of the token in flight; advanced by the LAST kernel of each token, so it
-                                // is stable (and readable ahead of griddepcontrol.wait) for the whole next token
-  unsigned long long* gen_count = nullptr;
-  int gen_cap = 0;
-  int nsplit = 1;
-  // plans
-  std::vector<b200::GemvPlan> p_qkv, p_o, p_gu, p_down;
-  b200::GemvPlan p_head{};
-  // graphs
-  cudaGraphExec_t g_step = nullptr;   // full token incl. lm_head + argmax
-  cudaGraphExec_t g_body = nullptr;   // embed + layers only (prefill tokens whose logits nobody reads)
-  // host mirrors
-  int64_t h_pos = 0;
-  int64_t h_gen = 0;
-  int launches_per_token = 0;   // kernels of a head token (what the graph g_step launches)
-  int launches_body = 0;        // kernels of a body-only token (g_body)
-  // batched prefill (tcgen05 GEMM path), workspace allocated on first use
-  uint8_t* pf_arena = nullptr;
-  int pf_chunk = 0;  // tokens the workspace holds
-  __nv_bfloat16 *pf_x = nullptr, *pf_h = nullptr, *pf_qkv = nullptr, *pf_attn = nullptr, *pf_gu = nullptr,
-                *pf_act = nullptr, *pf_t = nullptr;
-  bool use_prefill_gemm = true;
-  const void* final_norm_w = nullptr;
-  // tensor parallel
-  int tp_world = 1, tp_rank = 0;
-  bool shard_attn = true;
-  uint8_t* win[b200::kMaxTpWorld] = {nullptr};  // exchange windows of every rank as mapped here
-  unsigned long long* tp_epoch = nullptr;          // tokens completed (local)
-  __nv_bfloat16* x_alt = nullptr;                  // second hidden-state buffer (TP ping-pong)
-  const __nv_bfloat16* x_head = nullptr;           // residual the lm_head prologue reads (TP)
-  // ---- batched decode (B ≤ 8 sequences at the same position, the reference's left-padded batch): own KV caches and
-  // activations for all B sequences, GEMV plans that stream W once for the batch (gemv_batch.cu), own graphs.  Built on
-  // the first forward with B > 1 (engine_batch_prepare).
-  int batch = 1;                       // sequences of the most recent forward (decode / last_token follow it)
-  int b_cap = 0;                       // batch the buffers / plans / graphs below were built for
-  uint8_t* b_arena = nullptr;
-  __nv_bfloat16 *bk = nullptr, *bv = nullptr;                 // [B][L][max_ctx][Hkv][hd]
-  __nv_bfloat16 *bx = nullptr, *bqkv = nullptr, *battn = nullptr, *bact = nullptr, *blogits = nullptr;   // [B][·]
-  float* b_attn_ws = nullptr;
-  unsigned int* b_tickets = nullptr;
-  void* b_argmax_ws = nullptr;
-  int64_t* b_tok = nullptr;            // [B] token every sequence consumes next
-  int64_t* b_log = nullptr;            // [gen_cap][B] generated tokens
-  unsigned long long* b_cnt = nullptr; // [B] tokens generated per sequence (all equal)
-  int64_t hb_gen = 0;                  // host mirror of b_cnt
-  std::vector<b200::GemvPlan> bp_qkv, bp_o, bp_gu, bp_down;
-  b200::GemvPlan bp_head{};
-  cudaGraphExec_t gb_step = nullptr, gb_body = nullptr;
-  int b_launches = 0, b_launches_body = 0;
-  unsigned long long* trace = nullptr;  // B200_TRACE=1: [launch][8] globaltimer stamps of the last token
-  bool use_graph = true;
-  bool use_pdl = true;
-  // sampler (b200_engine_set_sampler): when active the last kernels of a head token are the device sampler instead of
-  // the argmax; u = Philox(seed, tokens generated so far)
-  bool sampler_on = false;
-  float s_temperature = 0.f, s_top_p = 1.f, s_min_p = 0.f;
-  int64_t s_top_k = 0;
-  unsigned long long s_seed = 0;
-  void* sample_ws = nullptr;
-  // async token pipeline (b200_engine_set_mailbox): ring in pinned host memory the argmax kernel posts tokens into
-  unsigned long long* mailbox = nullptr;
-  unsigned long long mailbox_cap = 1;
-};
+#include "engine.cuh"
 
 namespace b200 {
 
-static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 namespace {
 
@@ -879,6 +795,7 @@ int b200_engine_create_tp(const b200_model_desc* desc, const b200_weight_table* 
 
 void b200_engine_destroy(b200_engine* e) {
   if (!e) return;
+  if (e->stack) b200::stack_destroy(e);
   if (e->g_step) cudaGraphExecDestroy(e->g_step);
   if (e->g_body) cudaGraphExecDestroy(e->g_body);
   if (e->arena) cudaFree(e->arena);
@@ -891,6 +808,7 @@ void b200_engine_destroy(b200_engine* e) {
 int b200_engine_reset(b200_engine* e, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e, "engine_reset: null engine");
+  if (e->stack) return stack_reset(e, (cudaStream_t)stream);
   B200_CUDA(cudaMemsetAsync(e->pos, 0, 16, (cudaStream_t)stream));
   e->h_pos = 0;
   return B200_OK;
@@ -899,6 +817,7 @@ int b200_engine_reset(b200_engine* e, void* stream) {
 int b200_engine_seek(b200_engine* e, int64_t position, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e, "engine_seek: null engine");
+  if (e->stack) return stack_seek(e, position, (cudaStream_t)stream);
   if (position < 0 || position > e->h_pos) {
     set_error("engine_seek: position %lld is not inside the cached prefix [0, %lld]", (long long)position,
               (long long)e->h_pos);
@@ -915,6 +834,7 @@ int b200_engine_forward(b200_engine* e, const int64_t* ids, int64_t B, int64_t S
                         void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e && ids, "engine_forward: null argument");
+  if (e->stack) return stack_forward(e, ids, B, S, logits_out, logits_mode, (cudaStream_t)stream);
   B200_CHECK_ARG(B >= 1 && B <= kMaxBatch, "engine_forward: batch %lld not built (1 … %d sequences per step)", (long long)B,
                  kMaxBatch);
   B200_CHECK_ARG(S >= 1, "engine_forward: empty sequence");
@@ -997,6 +917,7 @@ int b200_engine_forward(b200_engine* e, const int64_t* ids, int64_t B, int64_t S
 int b200_engine_decode(b200_engine* e, int64_t n_steps, int64_t* tokens_out, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e && n_steps >= 0, "engine_decode: bad argument");
+  if (e->stack) return stack_decode(e, n_steps, tokens_out, (cudaStream_t)stream);
   B200_CHECK_ARG(n_steps <= e->gen_cap, "engine_decode: at most %d steps per call", e->gen_cap);
   if (e->h_pos + n_steps > e->d.max_ctx) {
     set_error("engine_decode: position %lld + %lld steps exceeds max_ctx %d", (long long)e->h_pos, (long long)n_steps,
@@ -1041,6 +962,7 @@ int b200_engine_decode(b200_engine* e, int64_t n_steps, int64_t* tokens_out, voi
 int b200_engine_last_token(b200_engine* e, int64_t* token_out, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e && token_out, "engine_last_token: null argument");
+  if (e->stack) return stack_last_token(e, token_out, (cudaStream_t)stream);
   if (e->batch > 1) {   // token_out [B]
     B200_CUDA(cudaMemcpyAsync(token_out, e->b_tok, (size_t)e->batch * 8, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     return B200_OK;
@@ -1071,6 +993,7 @@ int b200_engine_set_sampler(b200_engine* e, float temperature, int64_t top_k, fl
   e->s_top_p = top_p;
   e->s_min_p = min_p;
   e->s_seed = seed;
+  if (e->stack) return stack_set_sampler(e, (cudaStream_t)stream);
   if (e->use_graph) {
     cudaGraphExec_t fresh = nullptr;
     int rc = engine_capture(e, true, &fresh);
@@ -1084,6 +1007,10 @@ int b200_engine_set_sampler(b200_engine* e, float temperature, int64_t top_k, fl
 int b200_engine_set_mailbox(b200_engine* e, uint64_t* ring, int64_t capacity, void* stream) {
   using namespace b200;
   B200_CHECK_ARG(e, "engine_set_mailbox: null engine");
+  if (e->stack) {
+    set_error("engine_set_mailbox: stack engines keep a token log per slot; mailbox not built");
+    return B200_ERR_UNSUPPORTED;
+  }
   B200_CHECK_ARG(ring == nullptr || (capacity >= 2 && (reinterpret_cast<uintptr_t>(ring) & 7) == 0),
                  "engine_set_mailbox: ring must be 8-byte aligned with capacity >= 2");
   if (e->tp_world > 1) {
@@ -1131,6 +1058,7 @@ int64_t b200_engine_options(const b200_engine* e) {
 
 int64_t b200_engine_bytes_per_token(const b200_engine* e, int64_t ctx) {
   if (!e) return -1;
+  if (e->stack) return b200::stack_bytes_per_token(e, ctx);
   const b200_model_desc& d = e->d;
   const int64_t per_layer = (int64_t)(e->qdim + 2 * e->kvdim) * d.hidden + (int64_t)e->qdim * d.hidden +
                             3ll * e->I_l * d.hidden;

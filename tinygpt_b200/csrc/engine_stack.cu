@@ -1,0 +1,689 @@
+// engine_stack.cu — layer-stack models behind the engine handle: a model given as data (runs of layers, each an
+// attention mixer + optional gated feed-forward + optional token-table side input), sequence slots with their own KV
+// caches and positions, and ONE step function for every kind of step: the new tokens of all sequences of a step are
+// laid side by side as rows {token id, slot, position}; every kernel works on that row list, so a prompt, a part of a
+// prompt, a batch of unequal prompts and a batch of single decode tokens are the same code with a different list.
+//
+// Per run of a layer (parallel block, fp32 residual stream x):
+//   [x ← mix_in·[x; x0]]                       general GEMM over two operand sources, fp32 out (first run of a loop pass)
+//   h    = rmsnorm(x)·(offset + w)             fp32 → T
+//   proj = h·w_inᵀ + b_in                      ONE product for q | k | v | gate logits | ff gate | ff up
+//   K/V rows → this run's cache of the slot    (every pass of a looped layer is a run with a cache of its own)
+//   mid[:, 0 … heads·vdim)  = gated windowed attention(proj, cache)
+//   mid[:, off_act …)       = act(ff gate)·ff up
+//   x   += m · mid·w_outᵀ                      ONE product for o | ff down, summed in fp32 straight into the stream
+//   x   += m · rmsnorm(side_proj·(gelu(side_gate·x) ∘ table[token]))·w_side
+// then rmsnorm of the wanted rows only and the head product (fp32 logits + the bf16 copy argmax / sampler read).
+#include <algorithm>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "engine.cuh"
+
+namespace b200 {
+
+constexpr int kStackChunk = 4096;   // most rows one pass through the runs takes; longer steps go in several passes
+
+struct StackEngine {
+  b200_stack_desc d{};
+  std::vector<b200_stack_layer> layers;
+  std::vector<int> run_layer, run_mix;
+  int dtype = B200_BF16;
+  size_t esz = 2;
+  int gen_cap = 1 << 14;
+  // caches: [slot][run][max_ctx][kv_heads·dim] and [slot][run][max_ctx][kv_heads·vdim]
+  uint8_t* cache = nullptr;
+  uint8_t *kbase = nullptr, *vbase = nullptr;
+  std::vector<size_t> run_k_off, run_v_off;   // elements from the start of a slot
+  size_t k_slot = 0, v_slot = 0;              // elements per slot
+  // per-slot device state
+  uint8_t* state = nullptr;
+  int* pos_dev = nullptr;
+  int64_t* cur_tok = nullptr;
+  int64_t* gen_log = nullptr;
+  unsigned long long* gen_count = nullptr;
+  int* row_slot = nullptr;
+  void* argmax_ws = nullptr;
+  int64_t* amax_out = nullptr;
+  void* sample_ws = nullptr;
+  std::vector<int64_t> h_pos, h_gen;
+  std::vector<int> active;                    // slots of the batch decode / last_token follow, in row order
+  // workspace of a pass (grows)
+  uint8_t* ws = nullptr;
+  int ws_tok = 0, ws_rows = 0;
+  float *x = nullptr, *x_alt = nullptr, *x0 = nullptr, *y = nullptr, *logits = nullptr;
+  void *h = nullptr, *proj = nullptr, *mid = nullptr, *sg = nullptr, *hn = nullptr;
+  __nv_bfloat16* logits_bf = nullptr;
+  int32_t *m_tok = nullptr, *m_slot = nullptr, *m_pos = nullptr, *m_want = nullptr, *m_upd = nullptr;
+  int n_in_max = 0, k_out_max = 0;
+};
+
+namespace {
+
+// rows of a [B, S] id matrix (columns s0 … s0+cs) → the step's row list; positions continue each slot's cache
+__global__ void stack_meta_from_ids_kernel(const int64_t* __restrict__ ids, int B, int S, int s0, int cs,
+                                           const int* __restrict__ pos_dev, int32_t* tok, int32_t* slot, int32_t* pos) {
+  const int n = B * cs;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < n; e += gridDim.x * blockDim.x) {
+    const int b = e / cs, t = e % cs;
+    tok[e] = (int32_t)ids[(int64_t)b * S + s0 + t];
+    slot[e] = b;
+    pos[e] = pos_dev[b] + s0 + t;
+  }
+}
+// one decode token per active row: the slot's current token at the slot's position, which then advances
+__global__ void stack_meta_decode_kernel(const int* __restrict__ row_slot, int rows, int* pos_dev,
+                                         const int64_t* __restrict__ cur_tok, int32_t* tok, int32_t* slot, int32_t* pos,
+                                         int32_t* want) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int s = row_slot[r];
+  const int p = pos_dev[s];
+  tok[r] = (int32_t)cur_tok[s];
+  slot[r] = s;
+  pos[r] = p;
+  want[r] = r;
+  pos_dev[s] = p + 1;
+}
+// {slot, new position} pairs decided on the host
+__global__ void stack_set_pos_kernel(const int32_t* __restrict__ upd, int n, int* pos_dev) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) pos_dev[upd[2 * i]] = upd[2 * i + 1];
+}
+__global__ void stack_iota_last_kernel(int32_t* want, int B, int cs) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B) want[b] = b * cs + cs - 1;
+}
+__global__ void stack_iota_kernel(int32_t* want, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) want[i] = i;
+}
+
+}  // namespace
+
+static int stack_workspace(StackEngine* s, int tok, int rows) {
+  if (s->ws != nullptr && s->ws_tok >= tok && s->ws_rows >= rows) return B200_OK;
+  tok = std::max(tok, s->ws_tok);
+  rows = std::max(rows, s->ws_rows);
+  if (s->ws) {
+    B200_CUDA(cudaDeviceSynchronize());
+    cudaFree(s->ws);
+    s->ws = nullptr;
+  }
+  const b200_stack_desc& d = s->d;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off = align_up(off + bytes, 256);
+    return o;
+  };
+  const size_t W = d.width, T = tok;
+  const size_t o_x = take(T * W * 4), o_xa = take(T * W * 4), o_x0 = take(T * W * 4), o_y = take(T * W * 4);
+  const size_t o_h = take(T * W * s->esz), o_proj = take(T * s->n_in_max * s->esz);
+  const size_t o_mid = take(T * s->k_out_max * s->esz), o_sg = take(T * std::max(1, d.side_dim) * s->esz);
+  const size_t o_hn = take((size_t)rows * W * s->esz), o_lg = take((size_t)rows * d.vocab * 4);
+  const size_t o_lb = take((size_t)rows * d.vocab * 2);
+  const size_t o_meta = take((3 * T + rows + 2 * (size_t)d.max_slots) * 4);
+  B200_CUDA(cudaMalloc((void**)&s->ws, off));
+  B200_CUDA(cudaMemset(s->ws, 0, off));
+  s->ws_tok = tok;
+  s->ws_rows = rows;
+  s->x = (float*)(s->ws + o_x);
+  s->x_alt = (float*)(s->ws + o_xa);
+  s->x0 = (float*)(s->ws + o_x0);
+  s->y = (float*)(s->ws + o_y);
+  s->h = s->ws + o_h;
+  s->proj = s->ws + o_proj;
+  s->mid = s->ws + o_mid;
+  s->sg = s->ws + o_sg;
+  s->hn = s->ws + o_hn;
+  s->logits = (float*)(s->ws + o_lg);
+  s->logits_bf = (__nv_bfloat16*)(s->ws + o_lb);
+  s->m_tok = (int32_t*)(s->ws + o_meta);
+  s->m_slot = s->m_tok + T;
+  s->m_pos = s->m_slot + T;
+  s->m_want = s->m_pos + T;
+  s->m_upd = s->m_want + rows;
+  return B200_OK;
+}
+
+// One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
+static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  const b200_stack_desc& d = s->d;
+  const int W = d.width, dt = s->dtype;
+  int rc;
+  if ((rc = launch_stack_embed(s->x, s->x0, d.embed, s->m_tok, n_tok, d.vocab, W, d.embed_scale, dt, st)) != B200_OK)
+    return rc;
+  float *cur = s->x, *other = s->x_alt;
+  for (int r = 0; r < d.n_runs; ++r) {
+    const b200_stack_layer& L = s->layers[s->run_layer[r]];
+    if (s->run_mix[r]) {
+      StackGemm g;
+      g.a = cur; g.a2 = s->x0; g.lda = g.lda2 = W; g.k1 = W; g.a_f32 = true;
+      g.w = d.mix_in; g.M = n_tok; g.N = W; g.K = 2 * W;
+      g.epi = SEPI_STORE_F32; g.c = other; g.ldc = W;
+      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      std::swap(cur, other);
+    }
+    if ((rc = launch_stack_rmsnorm(s->h, cur, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, dt, st)) != B200_OK)
+      return rc;
+    {
+      StackGemm g;
+      g.a = s->h; g.lda = W; g.k1 = W;
+      g.w = L.w_in; g.bias = L.b_in; g.M = n_tok; g.N = L.n_in; g.K = W;
+      g.epi = SEPI_STORE; g.c = s->proj; g.ldc = L.n_in;
+      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+    }
+    StackAttn a;
+    a.a = L.attn;
+    a.proj = s->proj; a.ld_proj = L.n_in;
+    a.off_q = L.off_q; a.off_k = L.off_k; a.off_v = L.off_v; a.off_g = L.off_g;
+    a.kcache = s->kbase + s->run_k_off[r] * s->esz;
+    a.vcache = s->vbase + s->run_v_off[r] * s->esz;
+    a.k_slot_stride = (int64_t)s->k_slot; a.v_slot_stride = (int64_t)s->v_slot;
+    a.slot = s->m_slot; a.pos = s->m_pos; a.n_tok = n_tok;
+    a.out = s->mid; a.ld_out = L.k_out;
+    const int hv = L.attn.heads * L.attn.vdim;
+    if (hv != L.off_act || L.off_act + L.ff != L.k_out)   // padding columns meet zero weights: keep them finite
+      B200_CUDA(cudaMemsetAsync(s->mid, 0, (size_t)n_tok * L.k_out * s->esz, st));
+    if ((rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
+    if ((rc = launch_stack_attention(a, dt, st)) != B200_OK) return rc;
+    if (L.ff > 0) {
+      const uint8_t* p = (const uint8_t*)s->proj;
+      if ((rc = launch_stack_act_mul((uint8_t*)s->mid + (size_t)L.off_act * s->esz, L.k_out, p + (size_t)L.off_gate * s->esz,
+                                     p + (size_t)L.off_up * s->esz, L.n_in, n_tok, L.ff, L.ff_act, dt, st)) != B200_OK)
+        return rc;
+    }
+    {
+      StackGemm g;
+      g.a = s->mid; g.lda = L.k_out; g.k1 = L.k_out;
+      g.w = L.w_out; g.M = n_tok; g.N = W; g.K = L.k_out;
+      g.epi = SEPI_RESIDUAL; g.c = cur; g.ldc = W; g.mult = d.residual_mult;
+      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+    }
+    if (L.side_gate != nullptr) {
+      StackGemm g;
+      g.a = cur; g.lda = W; g.k1 = W; g.a_f32 = true;
+      g.w = L.side_gate; g.M = n_tok; g.N = d.side_dim; g.K = W;
+      g.epi = SEPI_ACT_TABLE; g.c = s->sg; g.ldc = d.side_dim;
+      g.table = d.side_table; g.tok = s->m_tok; g.table_ld = d.side_stride; g.table_col = L.side_col;
+      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      StackGemm p;
+      p.a = s->sg; p.lda = d.side_dim; p.k1 = d.side_dim;
+      p.w = L.side_proj; p.M = n_tok; p.N = W; p.K = d.side_dim;
+      p.epi = SEPI_STORE_F32; p.c = s->y; p.ldc = W;
+      if ((rc = launch_stack_gemm(p, dt, st)) != B200_OK) return rc;
+      if ((rc = launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st)) != B200_OK)
+        return rc;
+    }
+  }
+  if (n_rows > 0) {
+    if ((rc = launch_stack_rmsnorm(s->hn, cur, d.final_norm, s->m_want, n_rows, W, d.norm_eps, d.norm_offset, dt, st)) !=
+        B200_OK)
+      return rc;
+    StackGemm g;
+    g.a = s->hn; g.lda = W; g.k1 = W;
+    g.w = d.head; g.M = n_rows; g.N = d.vocab; g.K = W;
+    g.epi = SEPI_LOGITS; g.c = s->logits; g.ldc = d.vocab; g.c2 = s->logits_bf;
+    if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+  }
+  return B200_OK;
+}
+
+// greedy / sampled token of logits rows [row0, row0 + n) → the slots in `slots` (row order)
+static int stack_publish(b200_engine* e, int row0, const std::vector<int>& slots, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  const int n = (int)slots.size();
+  const __nv_bfloat16* lg = s->logits_bf + (size_t)row0 * s->d.vocab;
+  int rc;
+  if (e->sampler_on) {
+    for (int r = 0; r < n; ++r) {
+      ArgmaxPublish pub;
+      const int sl = slots[r];
+      pub.cur_tok = s->cur_tok + sl;
+      pub.gen_log = s->gen_log + (size_t)sl * s->gen_cap;
+      pub.gen_count = s->gen_count + sl;
+      pub.gen_cap = s->gen_cap;
+      if ((rc = launch_sample(nullptr, lg + (size_t)r * s->d.vocab, s->d.vocab, e->s_temperature, e->s_top_k, e->s_top_p,
+                              e->s_min_p, 0.f, s->sample_ws, st, &pub, e->s_seed, true)) != B200_OK)
+        return rc;
+    }
+  } else {
+    ArgmaxPublish pub;
+    pub.cur_tok = s->cur_tok;
+    pub.gen_log = s->gen_log;
+    pub.gen_count = s->gen_count;
+    pub.gen_cap = s->gen_cap;
+    pub.row_slot = s->row_slot;
+    if ((rc = launch_argmax(s->amax_out, lg, n, s->d.vocab, s->argmax_ws, st, false, &pub)) != B200_OK) return rc;
+  }
+  for (int sl : slots) s->h_gen[sl] += 1;
+  return B200_OK;
+}
+
+static int stack_set_active(StackEngine* s, const std::vector<int>& slots, cudaStream_t st) {
+  if (slots != s->active) {
+    s->active = slots;
+    B200_CUDA(cudaMemcpyAsync(s->row_slot, slots.data(), slots.size() * 4, cudaMemcpyHostToDevice, st));
+  }
+  return B200_OK;
+}
+
+void stack_destroy(b200_engine* e) {
+  StackEngine* s = e->stack;
+  if (!s) return;
+  if (s->cache) cudaFree(s->cache);
+  if (s->state) cudaFree(s->state);
+  if (s->ws) cudaFree(s->ws);
+  delete s;
+  e->stack = nullptr;
+}
+
+int stack_reset(b200_engine* e, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  B200_CUDA(cudaMemsetAsync(s->pos_dev, 0, (size_t)s->d.max_slots * 4, st));
+  std::fill(s->h_pos.begin(), s->h_pos.end(), 0);
+  e->h_pos = 0;
+  return B200_OK;
+}
+
+static int stack_push_positions(StackEngine* s, const std::vector<int32_t>& upd, cudaStream_t st) {
+  const int n = (int)upd.size() / 2;
+  if (n == 0) return B200_OK;
+  B200_CUDA(cudaMemcpyAsync(s->m_upd, upd.data(), upd.size() * 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA(launch_pdl(stack_set_pos_kernel, dim3((n + 63) / 64), dim3(64), 0, st, false, (const int32_t*)s->m_upd, n,
+                       s->pos_dev));
+  return B200_OK;
+}
+
+int stack_seek(b200_engine* e, int64_t position, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  // every slot of the active batch is rewound (they advance together under forward / decode)
+  std::vector<int> slots = s->active.empty() ? std::vector<int>{0} : s->active;
+  for (int sl : slots)
+    if (position < 0 || position > s->h_pos[sl]) {
+      set_error("engine_seek: position %lld is not inside the cached prefix [0, %lld] of slot %d", (long long)position,
+                (long long)s->h_pos[sl], sl);
+      return B200_ERR_STATE;
+    }
+  int rc = stack_workspace(s, 1, 1);
+  if (rc != B200_OK) return rc;
+  std::vector<int32_t> upd;
+  for (int sl : slots) {
+    upd.push_back(sl);
+    upd.push_back((int32_t)position);
+    s->h_pos[sl] = position;
+  }
+  e->h_pos = position;
+  return stack_push_positions(s, upd, st);
+}
+
+int stack_forward(b200_engine* e, const int64_t* ids, int64_t B, int64_t S, void* logits_out, int logits_mode,
+                  cudaStream_t st) {
+  StackEngine* s = e->stack;
+  const b200_stack_desc& d = s->d;
+  B200_CHECK_ARG(B >= 1 && B <= d.max_slots, "engine_forward: batch %lld exceeds the engine's %d slots", (long long)B,
+                 d.max_slots);
+  B200_CHECK_ARG(S >= 1, "engine_forward: empty sequence");
+  B200_CHECK_ARG(logits_mode == 0 || logits_mode == 1, "engine_forward: logits_mode must be 0 or 1");
+  for (int b = 0; b < B; ++b)
+    if (s->h_pos[b] + S > d.max_ctx) {
+      set_error("engine_forward: slot %d: position %lld + %lld tokens exceeds max_ctx %d", b, (long long)s->h_pos[b],
+                (long long)S, d.max_ctx);
+      return B200_ERR_STATE;
+    }
+  const bool all = logits_mode == 1 && logits_out != nullptr;
+  const int cs_max = std::max<int>(1, kStackChunk / (int)B);
+  int rc;
+  std::vector<int> slots((size_t)B);
+  for (int b = 0; b < B; ++b) slots[b] = b;
+  const int ws_tok = (int)std::min<int64_t>(S, cs_max) * (int)B;
+  if ((rc = stack_workspace(s, ws_tok, (all ? ws_tok : 0) + (int)B)) != B200_OK) return rc;
+  if ((rc = stack_set_active(s, slots, st)) != B200_OK) return rc;
+  const size_t vb = (size_t)d.vocab * 2;
+  int head_row0 = 0;   // first of the B rows that hold the sequences' last positions
+  for (int64_t s0 = 0; s0 < S; s0 += cs_max) {
+    const int cs = (int)std::min<int64_t>(cs_max, S - s0);
+    const int n_tok = cs * (int)B;
+    const bool last = s0 + cs == S;
+    B200_CUDA(launch_pdl(stack_meta_from_ids_kernel, dim3((n_tok + 255) / 256), dim3(256), 0, st, false, ids, (int)B, (int)S,
+                         (int)s0, cs, (const int*)s->pos_dev, s->m_tok, s->m_slot, s->m_pos));
+    // rows: every token of the chunk when all positions are asked for, then (last chunk) the B last positions
+    int n_rows = 0;
+    if (all) {
+      n_rows = n_tok;
+      B200_CUDA(launch_pdl(stack_iota_kernel, dim3((n_tok + 255) / 256), dim3(256), 0, st, false, s->m_want, n_tok));
+    }
+    if (last) {
+      head_row0 = n_rows;
+      B200_CUDA(launch_pdl(stack_iota_last_kernel, dim3(((int)B + 63) / 64), dim3(64), 0, st, false, s->m_want + n_rows,
+                           (int)B, cs));
+      n_rows += (int)B;
+    }
+    if ((rc = stack_pass(e, n_tok, n_rows, st)) != B200_OK) return rc;
+    if (all)   // rows are [b][t of this chunk] → logits_out [B][S][V]
+      B200_CUDA(cudaMemcpy2DAsync((uint8_t*)logits_out + (size_t)s0 * vb, (size_t)S * vb, s->logits_bf, (size_t)cs * vb,
+                                  (size_t)cs * vb, (size_t)B, cudaMemcpyDeviceToDevice, st));
+  }
+  if (!all && logits_out != nullptr)
+    B200_CUDA(cudaMemcpyAsync(logits_out, s->logits_bf, (size_t)B * vb, cudaMemcpyDeviceToDevice, st));
+  // the meta kernels read pos_dev + the column offset: advance only now that the whole matrix went through
+  std::vector<int32_t> upd;
+  for (int b = 0; b < B; ++b) {
+    s->h_pos[b] += S;
+    upd.push_back(b);
+    upd.push_back((int32_t)s->h_pos[b]);
+  }
+  if ((rc = stack_push_positions(s, upd, st)) != B200_OK) return rc;
+  e->h_pos = s->h_pos[0];
+  e->batch = (int)B;
+  // the greedy token of every sequence's last position becomes its slot's current token
+  return stack_publish(e, head_row0, slots, st);
+}
+
+int stack_decode(b200_engine* e, int64_t n_steps, int64_t* tokens_out, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  B200_CHECK_ARG(!s->active.empty(), "engine_decode: no active batch (run a forward or a greedy step first)");
+  B200_CHECK_ARG(n_steps <= s->gen_cap, "engine_decode: at most %d steps per call", s->gen_cap);
+  const int B = (int)s->active.size();
+  for (int sl : s->active)
+    if (s->h_pos[sl] + n_steps > s->d.max_ctx) {
+      set_error("engine_decode: slot %d: position %lld + %lld steps exceeds max_ctx %d", sl, (long long)s->h_pos[sl],
+                (long long)n_steps, s->d.max_ctx);
+      return B200_ERR_STATE;
+    }
+  int rc = stack_workspace(s, B, B);
+  if (rc != B200_OK) return rc;
+  std::vector<int64_t> first(B);
+  for (int r = 0; r < B; ++r) first[r] = s->h_gen[s->active[r]];
+  for (int64_t i = 0; i < n_steps; ++i) {
+    B200_CUDA(launch_pdl(stack_meta_decode_kernel, dim3((B + 63) / 64), dim3(64), 0, st, false, (const int*)s->row_slot, B,
+                         s->pos_dev, (const int64_t*)s->cur_tok, s->m_tok, s->m_slot, s->m_pos, s->m_want));
+    if ((rc = stack_pass(e, B, B, st)) != B200_OK) return rc;
+    if ((rc = stack_publish(e, 0, s->active, st)) != B200_OK) return rc;
+  }
+  for (int sl : s->active) s->h_pos[sl] += n_steps;
+  e->h_pos = s->h_pos[s->active[0]];
+  if (tokens_out != nullptr && n_steps > 0) {   // [n_steps][B] from the slots' own logs
+    for (int r = 0; r < B; ++r) {
+      const int64_t a = first[r] % s->gen_cap;
+      const int64_t n1 = std::min<int64_t>(n_steps, s->gen_cap - a);
+      const int64_t* log = s->gen_log + (size_t)s->active[r] * s->gen_cap;
+      B200_CUDA(cudaMemcpy2DAsync(tokens_out + r, (size_t)B * 8, log + a, 8, 8, (size_t)n1, cudaMemcpyDeviceToDevice, st));
+      if (n1 < n_steps)
+        B200_CUDA(cudaMemcpy2DAsync(tokens_out + n1 * B + r, (size_t)B * 8, log, 8, 8, (size_t)(n_steps - n1),
+                                    cudaMemcpyDeviceToDevice, st));
+    }
+  }
+  return B200_OK;
+}
+
+int stack_last_token(b200_engine* e, int64_t* token_out, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  B200_CHECK_ARG(!s->active.empty(), "engine_last_token: no active batch");
+  for (size_t r = 0; r < s->active.size(); ++r)
+    B200_CUDA(cudaMemcpyAsync(token_out + r, s->cur_tok + s->active[r], 8, cudaMemcpyDeviceToDevice, st));
+  return B200_OK;
+}
+
+int stack_set_sampler(b200_engine* e, cudaStream_t st) {
+  (void)e;
+  (void)st;   // nothing is captured: the next publication reads the engine's sampler fields
+  return B200_OK;
+}
+
+int64_t stack_bytes_per_token(const b200_engine* e, int64_t ctx) {
+  const StackEngine* s = e->stack;
+  const b200_stack_desc& d = s->d;
+  int64_t bytes = (int64_t)d.vocab * d.width * s->esz;
+  for (int r = 0; r < d.n_runs; ++r) {
+    const b200_stack_layer& L = s->layers[s->run_layer[r]];
+    bytes += ((int64_t)L.n_in * d.width + (int64_t)d.width * L.k_out) * s->esz;
+    if (s->run_mix[r]) bytes += 2ll * d.width * d.width * s->esz;
+    if (L.side_gate) bytes += 2ll * d.side_dim * d.width * s->esz;
+    int64_t keys = ctx + 1;
+    if (L.attn.window > 0) keys = std::min<int64_t>(keys, (int64_t)L.attn.window + L.attn.keep_first);
+    bytes += (keys + 1) * L.attn.kv_heads * (L.attn.dim + L.attn.vdim) * s->esz;
+  }
+  return bytes;
+}
+
+static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
+  B200_CHECK_ARG(desc && out, "engine_create_stack: null argument");
+  *out = nullptr;
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  const b200_stack_desc& d = *desc;
+  B200_CHECK_ARG(d.dtype == B200_BF16 || d.dtype == B200_F32, "engine_create_stack: unknown dtype %d", d.dtype);
+  B200_CHECK_ARG(d.block == B200_BLOCK_PARALLEL, "engine_create_stack: block kind %d not built", d.block);
+  B200_CHECK_ARG(d.width > 0 && d.vocab > 0 && d.n_layers > 0 && d.n_runs > 0 && d.max_ctx > 0 && d.max_slots > 0,
+                 "engine_create_stack: non-positive size");
+  B200_CHECK_ARG(d.run_layer_host && d.run_mix_host && d.layers_host && d.embed && d.final_norm && d.head,
+                 "engine_create_stack: null pointer");
+  b200_engine* e = new (std::nothrow) b200_engine();
+  StackEngine* s = new (std::nothrow) StackEngine();
+  if (!e || !s) {
+    delete e;
+    delete s;
+    set_error("engine_create_stack: out of host memory");
+    return B200_ERR_INVALID;
+  }
+  e->stack = s;
+  struct Guard {
+    b200_engine* e;
+    ~Guard() {
+      if (e) b200_engine_destroy(e);
+    }
+  } guard{e};
+  s->d = d;
+  s->dtype = d.dtype;
+  s->esz = d.dtype == B200_F32 ? 4 : 2;
+  s->layers.assign(d.layers_host, d.layers_host + d.n_layers);
+  s->run_layer.assign(d.run_layer_host, d.run_layer_host + d.n_runs);
+  s->run_mix.assign(d.run_mix_host, d.run_mix_host + d.n_runs);
+  s->d.layers_host = nullptr;
+  s->d.run_layer_host = s->d.run_mix_host = nullptr;
+  for (int l = 0; l < d.n_layers; ++l) {
+    const b200_stack_layer& L = s->layers[l];
+    const b200_attn_desc& a = L.attn;
+    B200_CHECK_ARG(a.heads > 0 && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.dim > 0 && a.vdim > 0 && a.window >= 0 &&
+                       a.keep_first >= 0,
+                   "engine_create_stack: layer %d: bad attention sizes", l);
+    B200_CHECK_ARG(a.vdim <= 256 && a.dim <= 1024, "engine_create_stack: layer %d: head sizes above 1024 / 256 not built", l);
+    B200_CHECK_ARG(L.norm && L.w_in && L.w_out && L.n_in > 0 && L.k_out > 0 && L.ff >= 0, "engine_create_stack: layer %d: null weight", l);
+    B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.kv_heads * a.dim <= L.n_in &&
+                       L.off_v + a.kv_heads * a.vdim <= L.n_in && (!a.out_gate || L.off_g + a.heads <= L.n_in) &&
+                       (L.ff == 0 || (L.off_gate + L.ff <= L.n_in && L.off_up + L.ff <= L.n_in)) &&
+                       a.heads * a.vdim <= L.off_act && L.off_act + L.ff <= L.k_out,
+                   "engine_create_stack: layer %d: segment offsets do not fit", l);
+    B200_CHECK_ARG(L.side_gate == nullptr || (L.side_proj && L.side_norm && d.side_table && d.side_dim > 0 &&
+                                              L.side_col + d.side_dim <= d.side_stride),
+                   "engine_create_stack: layer %d: incomplete side input", l);
+    s->n_in_max = std::max(s->n_in_max, L.n_in);
+    s->k_out_max = std::max(s->k_out_max, L.k_out);
+  }
+  s->run_k_off.resize(d.n_runs);
+  s->run_v_off.resize(d.n_runs);
+  for (int r = 0; r < d.n_runs; ++r) {
+    B200_CHECK_ARG(s->run_layer[r] >= 0 && s->run_layer[r] < d.n_layers, "engine_create_stack: run %d names layer %d", r,
+                   s->run_layer[r]);
+    B200_CHECK_ARG(!s->run_mix[r] || d.mix_in, "engine_create_stack: run %d mixes the embedding in but mix_in is null", r);
+    const b200_attn_desc& a = s->layers[s->run_layer[r]].attn;
+    s->run_k_off[r] = s->k_slot;
+    s->run_v_off[r] = s->v_slot;
+    s->k_slot += (size_t)d.max_ctx * a.kv_heads * a.dim;
+    s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
+  }
+  B200_CUDA(cudaDeviceSynchronize());   // weights may still be in flight on the loader's stream
+  const size_t kb = align_up(s->k_slot * d.max_slots * s->esz, 256), vb = align_up(s->v_slot * d.max_slots * s->esz, 256);
+  B200_CUDA(cudaMalloc((void**)&s->cache, kb + vb));
+  s->kbase = s->cache;
+  s->vbase = s->cache + kb;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t o = off;
+    off = align_up(off + bytes, 256);
+    return o;
+  };
+  const size_t n = d.max_slots;
+  const size_t o_pos = take(n * 4), o_tok = take(n * 8), o_log = take(n * s->gen_cap * 8), o_cnt = take(n * 8);
+  const size_t o_rs = take(n * 4), o_amax = take((size_t)argmax_workspace_bytes((int64_t)n, d.vocab) + n * 8 + 16);
+  const size_t o_smp = take((size_t)sample_workspace_bytes());
+  B200_CUDA(cudaMalloc((void**)&s->state, off));
+  B200_CUDA(cudaMemset(s->state, 0, off));
+  s->pos_dev = (int*)(s->state + o_pos);
+  s->cur_tok = (int64_t*)(s->state + o_tok);
+  s->gen_log = (int64_t*)(s->state + o_log);
+  s->gen_count = (unsigned long long*)(s->state + o_cnt);
+  s->row_slot = (int*)(s->state + o_rs);
+  s->argmax_ws = s->state + o_amax;
+  s->amax_out = (int64_t*)((uint8_t*)s->argmax_ws + argmax_workspace_bytes((int64_t)n, d.vocab));
+  s->sample_ws = s->state + o_smp;
+  s->h_pos.assign(n, 0);
+  s->h_gen.assign(n, 0);
+  e->d.vocab = d.vocab;
+  e->d.hidden = d.width;
+  e->d.max_ctx = d.max_ctx;
+  e->d.layers = d.n_layers;
+  e->V_l = d.vocab;
+  e->use_graph = false;
+  e->use_pdl = false;
+  guard.e = nullptr;
+  *out = e;
+  return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_engine_create_stack(const b200_stack_desc* desc, b200_engine** out) { return b200::stack_build(desc, out); }
+
+int b200_engine_step(b200_engine* e, int64_t n_seq, const int32_t* slots, const int32_t* counts, const int64_t* ids,
+                     int64_t n_want, const int32_t* want, float* logits_out, int greedy, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(e && slots && counts && ids && n_seq >= 1, "engine_step: null argument");
+  if (!e->stack) {
+    set_error("engine_step: ragged steps over sequence slots are built for stack engines; Llama-family engines take "
+              "b200_engine_forward");
+    return B200_ERR_UNSUPPORTED;
+  }
+  B200_CHECK_ARG(n_want == 0 || (want && logits_out), "engine_step: wanted rows without an output buffer");
+  StackEngine* s = e->stack;
+  const b200_stack_desc& d = s->d;
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t total = 0;
+  std::vector<char> seen(d.max_slots, 0);
+  for (int64_t i = 0; i < n_seq; ++i) {
+    B200_CHECK_ARG(slots[i] >= 0 && slots[i] < d.max_slots && !seen[slots[i]], "engine_step: bad or repeated slot %d", slots[i]);
+    seen[slots[i]] = 1;
+    B200_CHECK_ARG(counts[i] >= 1, "engine_step: sequence %lld brings no token", (long long)i);
+    if (s->h_pos[slots[i]] + counts[i] > d.max_ctx) {
+      set_error("engine_step: slot %d: position %lld + %d tokens exceeds max_ctx %d", slots[i], (long long)s->h_pos[slots[i]],
+                counts[i], d.max_ctx);
+      return B200_ERR_STATE;
+    }
+    total += counts[i];
+  }
+  for (int64_t i = 0; i < n_want; ++i)
+    B200_CHECK_ARG(want[i] >= 0 && want[i] < total, "engine_step: wanted row %d outside the step's %lld tokens", want[i],
+                   (long long)total);
+  // the row list on the host: token, slot, position
+  std::vector<int32_t> tok(total), slot(total), pos(total), last(n_seq);
+  {
+    int64_t t = 0;
+    for (int64_t i = 0; i < n_seq; ++i) {
+      for (int c = 0; c < counts[i]; ++c, ++t) {
+        tok[t] = (int32_t)ids[t];
+        slot[t] = slots[i];
+        pos[t] = (int32_t)s->h_pos[slots[i]] + c;
+      }
+      last[i] = (int32_t)t - 1;
+    }
+  }
+  const int chunk = kStackChunk;
+  int rc;
+  const int ws_tok = (int)std::min<int64_t>(total, chunk);
+  if ((rc = stack_workspace(s, ws_tok, (int)std::min<int64_t>(n_want + (greedy ? n_seq : 0), (int64_t)ws_tok + n_seq) + 1)) != B200_OK)
+    return rc;
+  std::vector<int> act_slots(slots, slots + n_seq);
+  if (greedy && (rc = stack_set_active(s, act_slots, st)) != B200_OK) return rc;
+  const size_t vb4 = (size_t)d.vocab * 4;
+  std::vector<int32_t> meta;
+  for (int64_t c0 = 0; c0 < total; c0 += chunk) {
+    const int n_tok = (int)std::min<int64_t>(chunk, total - c0);
+    // wanted rows of this chunk (in the caller's order), then — on the last chunk of a greedy step — the last rows
+    std::vector<int32_t> rows;
+    std::vector<int64_t> dest;
+    for (int64_t i = 0; i < n_want; ++i)
+      if (want[i] >= c0 && want[i] < c0 + n_tok) {
+        rows.push_back((int32_t)(want[i] - c0));
+        dest.push_back(i);
+      }
+    const int n_user = (int)rows.size();
+    const bool tail = c0 + n_tok == total;
+    if (greedy && tail) {
+      // a sequence whose last token fell into an earlier chunk cannot happen: chunks follow the row order and the
+      // last rows of all sequences but the final one may lie before c0 — those are recomputed from the cache
+      for (int64_t i = 0; i < n_seq; ++i) B200_CHECK_ARG(last[i] >= c0, "engine_step: greedy steps take at most %d tokens", chunk);
+      for (int64_t i = 0; i < n_seq; ++i) rows.push_back((int32_t)(last[i] - c0));
+    }
+    const int n_rows = (int)rows.size();
+    if ((rc = stack_workspace(s, n_tok, std::max(1, n_rows))) != B200_OK) return rc;
+    meta.assign(tok.begin() + c0, tok.begin() + c0 + n_tok);
+    B200_CUDA(cudaMemcpyAsync(s->m_tok, meta.data(), (size_t)n_tok * 4, cudaMemcpyHostToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(s->m_slot, slot.data() + c0, (size_t)n_tok * 4, cudaMemcpyHostToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(s->m_pos, pos.data() + c0, (size_t)n_tok * 4, cudaMemcpyHostToDevice, st));
+    if (n_rows > 0) B200_CUDA(cudaMemcpyAsync(s->m_want, rows.data(), (size_t)n_rows * 4, cudaMemcpyHostToDevice, st));
+    if ((rc = stack_pass(e, n_tok, n_rows, st)) != B200_OK) return rc;
+    for (int r = 0; r < n_user;) {   // runs of consecutive destination rows leave in one copy
+      int r1 = r + 1;
+      while (r1 < n_user && dest[r1] == dest[r1 - 1] + 1) ++r1;
+      B200_CUDA(cudaMemcpyAsync((uint8_t*)logits_out + (size_t)dest[r] * vb4, (uint8_t*)s->logits + (size_t)r * vb4,
+                                (size_t)(r1 - r) * vb4, cudaMemcpyDeviceToDevice, st));
+      r = r1;
+    }
+    if (greedy && tail && (rc = stack_publish(e, n_user, act_slots, st)) != B200_OK) return rc;
+  }
+  std::vector<int32_t> upd;
+  for (int64_t i = 0; i < n_seq; ++i) {
+    s->h_pos[slots[i]] += counts[i];
+    upd.push_back(slots[i]);
+    upd.push_back((int32_t)s->h_pos[slots[i]]);
+  }
+  e->h_pos = s->h_pos[slots[0]];
+  if (greedy) e->batch = (int)n_seq;
+  return stack_push_positions(s, upd, st);
+}
+
+int b200_engine_slot_reset(b200_engine* e, int64_t slot, void* stream) {
+  using namespace b200;
+  B200_CHECK_ARG(e && e->stack, "engine_slot_reset: not a stack engine");
+  StackEngine* s = e->stack;
+  B200_CHECK_ARG(slot >= 0 && slot < s->d.max_slots, "engine_slot_reset: slot %lld of %d", (long long)slot, s->d.max_slots);
+  int rc = stack_workspace(s, 1, 1);
+  if (rc != B200_OK) return rc;
+  s->h_pos[slot] = 0;
+  auto it = std::find(s->active.begin(), s->active.end(), (int)slot);
+  if (it != s->active.end()) {   // the sequence leaves the active batch; the others go on
+    std::vector<int> rest = s->active;
+    rest.erase(rest.begin() + (it - s->active.begin()));
+    s->active.clear();
+    if (!rest.empty() && (rc = stack_set_active(s, rest, (cudaStream_t)stream)) != B200_OK) return rc;
+  }
+  return stack_push_positions(s, {(int32_t)slot, 0}, (cudaStream_t)stream);
+}
+
+int64_t b200_engine_slot_position(const b200_engine* e, int64_t slot) {
+  if (!e || !e->stack || slot < 0 || slot >= e->stack->d.max_slots) return -1;
+  return e->stack->h_pos[slot];
+}
+
+int64_t b200_engine_max_slots(const b200_engine* e) {
+  if (!e) return -1;
+  return e->stack ? e->stack->d.max_slots : b200::kMaxBatch;
+}
+
+}  // extern "C"

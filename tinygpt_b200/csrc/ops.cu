@@ -217,6 +217,14 @@ __global__ void __launch_bounds__(256) argmax_kernel(int64_t* __restrict__ out, 
         asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(c), "r"(__float_as_uint(v)), "r"(tag) : "memory");
         asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(c + 1), "r"(gidx), "r"(tag) : "memory");
       }
+    } else if (pub.cur_tok != nullptr && pub.row_slot != nullptr) {
+      // slot engine: row r belongs to sequence slot row_slot[r]; its token becomes that slot's next input and joins the
+      // slot's own log (positions are advanced by the step that consumes the token)
+      const int s = pub.row_slot[row];
+      pub.cur_tok[s] = idx;
+      const unsigned long long c = pub.gen_count[s];
+      pub.gen_log[(size_t)s * (size_t)pub.gen_cap + (size_t)(c % (unsigned long long)pub.gen_cap)] = idx;
+      pub.gen_count[s] = c + 1;
     } else if (pub.cur_tok != nullptr && pub.batch_rows > 1) {
       // batched engine: every row (sequence) publishes its own token; row 0 advances the shared position
       pub.cur_tok[row] = idx;

@@ -24,6 +24,8 @@ struct ArgmaxPublish {
   unsigned long long* gen_count = nullptr;
   int gen_cap = 1;
   int batch_rows = 0;   // > 1: per-row publication (see above); the log is [gen_cap][batch_rows]
+  const int* row_slot = nullptr;   // slot engines: row r publishes into cur_tok / gen_count [row_slot[r]] and the log
+                                   // [slot][gen_cap]; nothing advances a position
   // tensor parallel (vocabulary-sharded lm_head): instead of publishing, push (max logit, GLOBAL index) into every
   // rank's candidate slot and bump its arrival counter; tp_finish_kernel (engine.cu) picks the winner.
   // async token pipeline: ring in pinned, device-mapped host memory (b200_engine_set_mailbox); null = none

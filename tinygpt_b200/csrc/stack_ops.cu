@@ -1,0 +1,358 @@
+// stack_ops.cu — the layer-stack engine's mechanisms as plain kernels: any shape, storage type T = bf16 or fp32, fp32
+// arithmetic for norms, softmax, gates and everything that touches the residual stream.  These are the kernels every
+// shape can fall back on; the tensor-core GEMM (gemm.cu) and the weight-streaming GEMV (gemv.cu) take over the matrix
+// products whose shapes they accept (engine_stack.cu decides per product).
+#include "stack.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ T cvt(float v);
+template <> __device__ __forceinline__ float cvt<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+// the value a T-typed operand carries when its source is fp32
+template <typename T> __device__ __forceinline__ float as_operand(float v);
+template <> __device__ __forceinline__ float as_operand<float>(float v) { return v; }
+template <> __device__ __forceinline__ float as_operand<__nv_bfloat16>(float v) { return round_bf16(v); }
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+  const float c = 0.7978845608028654f;  // sqrt(2/pi)
+  return 0.5f * z * (1.f + tanhf(c * (z + 0.044715f * z * z * z)));
+}
+__device__ __forceinline__ float silu(float z) { return z / (1.f + expf(-z)); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  __syncthreads();
+  return tot;
+}
+
+// ------------------------------------------------------------------------------------------------------- general GEMM
+// 64 × 64 output tile per CTA, 16-wide k slices through shared memory (as fp32), 4 × 4 outputs per thread, fp32 FMA.
+// bf16 × bf16 products are exact in fp32, so T = bf16 gives "bf16 operands, fp32 accumulation"; T = fp32 is a true fp32
+// product (no reduced-precision matrix mode).
+constexpr int kBM = 64, kBN = 64, kBK = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(256) stack_gemm_kernel(const StackGemm g) {
+  __shared__ float As[kBK][kBM + 4];
+  __shared__ float Ws[kBK][kBN + 4];
+  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const T* W = static_cast<const T*>(g.w);
+  for (int k0 = 0; k0 < g.K; k0 += kBK) {
+    for (int e = threadIdx.x; e < kBM * kBK; e += 256) {
+      const int r = e / kBK, c = e % kBK;
+      const int m = m0 + r, k = k0 + c;
+      float v = 0.f;
+      if (m < g.M && k < g.K) {
+        const bool first = k < g.k1;
+        const void* src = first ? g.a : g.a2;
+        const int64_t idx = first ? (int64_t)m * g.lda + k : (int64_t)m * g.lda2 + (k - g.k1);
+        v = g.a_f32 ? as_operand<T>(static_cast<const float*>(src)[idx]) : ldf<T>(static_cast<const T*>(src) + idx);
+      }
+      As[c][r] = v;
+      const int n = n0 + r;
+      Ws[c][r] = (n < g.N && k < g.K) ? ldf<T>(W + (int64_t)n * g.K + k) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < kBK; ++c) {
+      float a[4], w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[c][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[j] = Ws[c][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j];
+      if (g.bias != nullptr) v += g.bias[n];
+      const int64_t o = (int64_t)m * g.ldc + n;
+      switch (g.epi) {
+        case SEPI_STORE: static_cast<T*>(g.c)[o] = cvt<T>(v); break;
+        case SEPI_STORE_F32: static_cast<float*>(g.c)[o] = v; break;
+        case SEPI_RESIDUAL: static_cast<float*>(g.c)[o] += g.mult * v; break;
+        case SEPI_ACT_TABLE: {
+          const float e = ldf<T>(static_cast<const T*>(g.table) + (int64_t)g.tok[m] * g.table_ld + g.table_col + n);
+          static_cast<T*>(g.c)[o] = cvt<T>(gelu_tanh(v) * e);
+          break;
+        }
+        default:
+          static_cast<float*>(g.c)[o] = v;
+          if (g.c2 != nullptr) g.c2[o] = __float2bfloat16_rn(v);
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------------------------- norms
+template <typename T>
+__global__ void __launch_bounds__(256) stack_rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
+                                                            const float* __restrict__ w, const int32_t* __restrict__ rows,
+                                                            int dim, float eps, float offset) {
+  __shared__ float red[8];
+  const int64_t src = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  const float* xr = x + src * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += xr[i] * xr[i];
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+  T* yr = y + (int64_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) yr[i] = cvt<T>(xr[i] * inv * (offset + w[i]));
+}
+
+__global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ x, const float* __restrict__ y,
+                                                            const float* __restrict__ w, int dim, float eps, float mult) {
+  __shared__ float red[8];
+  const float* yr = y + (int64_t)blockIdx.x * dim;
+  float* xr = x + (int64_t)blockIdx.x * dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += yr[i] * yr[i];
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += mult * (yr[i] * inv * w[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) stack_act_mul_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ g,
+                                                            const T* __restrict__ u, int64_t ld_gu, int n, int act,
+                                                            int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / n;
+    const int j = (int)(e % n);
+    const float gv = ldf<T>(g + r * ld_gu + j), uv = ldf<T>(u + r * ld_gu + j);
+    // the activation is a value of type T before it meets the other factor
+    const float a = as_operand<T>(act == B200_ACT_SILU ? silu(gv) : gelu_tanh(gv));
+    y[r * ld_y + j] = cvt<T>(a * uv);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) stack_embed_kernel(float* __restrict__ x, float* __restrict__ x0,
+                                                          const T* __restrict__ embed, const int32_t* __restrict__ tok,
+                                                          int vocab, int width, float scale) {
+  int id = tok[blockIdx.x];
+  if (id < 0 || id >= vocab) id = 0;
+  const T* row = embed + (int64_t)id * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = ldf<T>(row + i) * scale;
+    x[(int64_t)blockIdx.x * width + i] = v;
+    x0[(int64_t)blockIdx.x * width + i] = v;
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------- attention
+template <typename T>
+__global__ void __launch_bounds__(128) stack_kv_store_kernel(const StackAttn p) {
+  const int t = blockIdx.x;
+  const int nk = p.a.kv_heads * p.a.dim, nv = p.a.kv_heads * p.a.vdim;
+  const T* row = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  T* kd = static_cast<T*>(p.kcache) + (int64_t)p.slot[t] * p.k_slot_stride + (int64_t)p.pos[t] * nk;
+  T* vd = static_cast<T*>(p.vcache) + (int64_t)p.slot[t] * p.v_slot_stride + (int64_t)p.pos[t] * nv;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) kd[i] = row[p.off_k + i];
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) vd[i] = row[p.off_v + i];
+}
+
+// One warp per (token, query head).  The visible keys of a query at position i are the kept first rows
+// [0, min(keep_first, lo)) followed by the window [lo, i], lo = max(0, i − window + 1) (window 0: lo = 0).  The warp
+// walks that list 32 keys at a time: lane j scores key j (fp32 dot, times scale), the chunk joins an online softmax,
+// then the lanes turn to the value columns (lane + 32·r) and add the chunk's 32 weighted rows.
+template <typename T, int VR>
+__global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
+  extern __shared__ float qs_all[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
+  const int t = (int)(pair / p.a.heads), h = (int)(pair % p.a.heads);
+  if (t >= p.n_tok) return;
+  const int dim = p.a.dim, vdim = p.a.vdim;
+  float* qs = qs_all + warp * dim;
+  const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  for (int d = lane; d < dim; d += 32) qs[d] = ldf<T>(prow + p.off_q + h * dim + d);
+  __syncwarp();
+  const int slot = p.slot[t], i = p.pos[t];
+  const int kvh = h / (p.a.heads / p.a.kv_heads);
+  const int64_t krs = (int64_t)p.a.kv_heads * dim, vrs = (int64_t)p.a.kv_heads * vdim;
+  const T* kb = static_cast<const T*>(p.kcache) + (int64_t)slot * p.k_slot_stride + kvh * dim;
+  const T* vb = static_cast<const T*>(p.vcache) + (int64_t)slot * p.v_slot_stride + kvh * vdim;
+  const int lo = p.a.window > 0 ? max(0, i - p.a.window + 1) : 0;
+  const int na = min(p.a.keep_first, lo);
+  const int total = na + (i - lo + 1);
+  float m = -INFINITY, l = 0.f, acc[VR];
+#pragma unroll
+  for (int r = 0; r < VR; ++r) acc[r] = 0.f;
+  for (int c0 = 0; c0 < total; c0 += 32) {
+    const int idx = c0 + lane;
+    const bool valid = idx < total;
+    const int j = idx < na ? idx : lo + (idx - na);
+    float s = -INFINITY;
+    if (valid) {
+      const T* kr = kb + (int64_t)j * krs;
+      float dot = 0.f;
+      for (int d = 0; d < dim; ++d) dot = fmaf(qs[d], ldf<T>(kr + d), dot);
+      s = dot * p.a.scale;
+    }
+    const float mn = fmaxf(m, warp_max(s));
+    const float corr = m == -INFINITY ? 0.f : expf(m - mn);
+    const float pj = valid ? expf(s - mn) : 0.f;
+    l = l * corr + warp_sum(pj);
+#pragma unroll
+    for (int r = 0; r < VR; ++r) acc[r] *= corr;
+    const int cn = min(32, total - c0);
+    for (int jj = 0; jj < cn; ++jj) {
+      const float pw = __shfl_sync(0xffffffffu, pj, jj);
+      const int jr = __shfl_sync(0xffffffffu, j, jj);
+      const T* vr = vb + (int64_t)jr * vrs;
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < vdim) acc[r] = fmaf(pw, ldf<T>(vr + d), acc[r]);
+      }
+    }
+    m = mn;
+  }
+  float gate = 1.f;
+  if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
+  T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
+#pragma unroll
+  for (int r = 0; r < VR; ++r) {
+    const int d = lane + 32 * r;
+    if (d < vdim) orow[d] = cvt<T>(acc[r] / l * gate);
+  }
+}
+
+inline int grid_cap(int64_t n, int block) {
+  int64_t g = (n + block - 1) / block;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(g, 148 * 16));
+}
+
+}  // namespace
+
+#define STACK_DTYPE_CHECK(dtype) \
+  B200_CHECK_ARG((dtype) == B200_BF16 || (dtype) == B200_F32, "stack op: unknown dtype %d", (int)(dtype))
+
+int launch_stack_gemm(const StackGemm& g, int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(g.a && g.w && g.c && g.M > 0 && g.N > 0 && g.K > 0, "stack gemm: bad arguments M=%d N=%d K=%d", g.M, g.N,
+                 g.K);
+  B200_CHECK_ARG(g.k1 == g.K || g.a2 != nullptr, "stack gemm: second operand source missing");
+  B200_CHECK_ARG(g.epi != SEPI_ACT_TABLE || (g.table && g.tok), "stack gemm: table epilogue without a table");
+  const dim3 grid((g.N + kBN - 1) / kBN, (g.M + kBM - 1) / kBM);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_gemm_kernel<float>, grid, dim3(256), 0, st, false, g));
+  else B200_CUDA(launch_pdl(stack_gemm_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, false, g));
+  return B200_OK;
+}
+
+int launch_stack_rmsnorm(void* y, const float* x, const float* w, const int32_t* rows, int64_t n_rows, int dim, float eps,
+                         float offset, int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(y && x && w && n_rows > 0 && dim > 0, "stack rmsnorm: bad arguments");
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<float>, dim3((unsigned)n_rows), dim3(256), 0, st, false, (float*)y, x, w, rows,
+                         dim, eps, offset));
+  else
+    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(256), 0, st, false,
+                         (__nv_bfloat16*)y, x, w, rows, dim, eps, offset));
+  return B200_OK;
+}
+
+int launch_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int dim, float eps, float mult,
+                         cudaStream_t st) {
+  B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
+  B200_CUDA(launch_pdl(stack_rms_add_kernel, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps, mult));
+  return B200_OK;
+}
+
+int launch_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, int64_t ld_gu, int64_t rows, int n, int act,
+                         int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(y && g && u && rows > 0 && n > 0, "stack act_mul: bad arguments");
+  B200_CHECK_ARG(act == B200_ACT_GELU_TANH || act == B200_ACT_SILU, "stack act_mul: unknown activation %d", act);
+  const int64_t total = rows * n;
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_act_mul_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, (float*)y, ld_y,
+                         (const float*)g, (const float*)u, ld_gu, n, act, total));
+  else
+    B200_CUDA(launch_pdl(stack_act_mul_kernel<__nv_bfloat16>, dim3(grid_cap(total, 256)), dim3(256), 0, st, false,
+                         (__nv_bfloat16*)y, ld_y, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, ld_gu, n, act, total));
+  return B200_OK;
+}
+
+int launch_stack_embed(float* x, float* x0, const void* embed, const int32_t* tok, int64_t n_tok, int vocab, int width,
+                       float scale, int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(x && x0 && embed && tok && n_tok > 0, "stack embed: bad arguments");
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_embed_kernel<float>, dim3((unsigned)n_tok), dim3(128), 0, st, false, x, x0,
+                         (const float*)embed, tok, vocab, width, scale));
+  else
+    B200_CUDA(launch_pdl(stack_embed_kernel<__nv_bfloat16>, dim3((unsigned)n_tok), dim3(128), 0, st, false, x, x0,
+                         (const __nv_bfloat16*)embed, tok, vocab, width, scale));
+  return B200_OK;
+}
+
+static int check_attn(const StackAttn& p) {
+  const b200_attn_desc& a = p.a;
+  B200_CHECK_ARG(a.heads > 0 && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.dim > 0 && a.vdim > 0,
+                 "stack attention: bad head counts / sizes (heads %d, kv_heads %d, dim %d, vdim %d)", a.heads, a.kv_heads,
+                 a.dim, a.vdim);
+  B200_CHECK_ARG(a.window >= 0 && a.keep_first >= 0, "stack attention: negative window");
+  B200_CHECK_ARG(a.vdim <= 256 && a.dim <= 1024, "stack attention: head sizes above 1024 / 256 are not built");
+  B200_CHECK_ARG(p.proj && p.kcache && p.vcache && p.slot && p.pos && p.n_tok > 0, "stack attention: null argument");
+  return B200_OK;
+}
+
+int launch_stack_kv_store(const StackAttn& p, int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  int rc = check_attn(p);
+  if (rc != B200_OK) return rc;
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_kv_store_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, false, p));
+  else B200_CUDA(launch_pdl(stack_kv_store_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, false, p));
+  return B200_OK;
+}
+
+template <typename T>
+static cudaError_t launch_attn_t(const StackAttn& p, cudaStream_t st) {
+  const int64_t pairs = (int64_t)p.n_tok * p.a.heads;
+  const dim3 grid((unsigned)((pairs + 3) / 4));
+  const size_t smem = (size_t)4 * p.a.dim * sizeof(float);
+  const int vr = (p.a.vdim + 31) / 32;
+  if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 2) return launch_pdl(stack_attn_kernel<T, 2>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 4) return launch_pdl(stack_attn_kernel<T, 4>, grid, dim3(128), smem, st, false, p);
+  return launch_pdl(stack_attn_kernel<T, 8>, grid, dim3(128), smem, st, false, p);
+}
+
+int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
+  STACK_DTYPE_CHECK(dtype);
+  int rc = check_attn(p);
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(p.out != nullptr, "stack attention: null output");
+  if (dtype == B200_F32) B200_CUDA(launch_attn_t<float>(p, st));
+  else B200_CUDA(launch_attn_t<__nv_bfloat16>(p, st));
+  return B200_OK;
+}
+
+}  // namespace b200

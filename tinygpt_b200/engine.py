@@ -17,7 +17,8 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import models
-from ._lib import B200Error, LayerWeights, ModelDesc, WeightTable, check, lib, require_device
+from ._lib import (AttnDesc, B200Error, LayerWeights, ModelDesc, StackDesc, StackLayer, WeightTable, check, lib,
+                   require_device)
 
 
 def align_prompts(token_lists, context_size: int, pad_token: int):
@@ -38,6 +39,40 @@ def align_prompts(token_lists, context_size: int, pad_token: int):
     return ids, mask
 
 
+class SequenceSlots:
+    """Host-side owner of an engine's sequence slots: a request name gets the lowest free slot when it first appears
+    and gives it back when it ends; a freed slot is handed out again (its cache rows are simply overwritten)."""
+
+    def __init__(self, n_slots: int):
+        self.n_slots = int(n_slots)
+        self._free = list(range(self.n_slots))
+        self._of: Dict[object, int] = {}
+
+    def __contains__(self, name) -> bool:
+        return name in self._of
+
+    def __len__(self) -> int:
+        return len(self._of)
+
+    def slot(self, name) -> int:
+        return self._of[name]
+
+    def acquire(self, name) -> int:
+        if name in self._of:
+            return self._of[name]
+        if not self._free:
+            raise B200Error(f"no free sequence slot for {name!r}: all {self.n_slots} are taken")
+        self._free.sort()
+        s = self._free.pop(0)
+        self._of[name] = s
+        return s
+
+    def release(self, name) -> int:
+        s = self._of.pop(name)
+        self._free.append(s)
+        return s
+
+
 class DecodeEngine:
     """Whole-token engine for ONE sequence (batch 1) on the current CUDA device.
 
@@ -47,6 +82,10 @@ class DecodeEngine:
     def __init__(self, spec: models.ModelSpec, weights: Dict[str, torch.Tensor], rope_table: Optional[torch.Tensor] = None):
         require_device()
         self.spec = spec
+        self.is_stack = isinstance(spec, models.StackSpec)
+        if self.is_stack:
+            self._init_stack(spec, weights)
+            return
         dev = weights["model.embed_tokens.weight"].device
         if dev.type != "cuda":
             raise B200Error("DecodeEngine: weights must be on a CUDA device (no CPU path)")
@@ -89,6 +128,104 @@ class DecodeEngine:
                          spec.max_ctx, spec.rms_eps, int(spec.qkv_bias), int(spec.qk_norm), rank, world,
                          int(shard_attn))
         return desc, table
+
+    def _init_stack(self, spec: "models.StackSpec", weights: Dict[str, torch.Tensor]) -> None:
+        """Layer-stack model (models.StackSpec; weights from models.pack_stack_weights / loader.load_stack_checkpoint):
+        the description travels as data through b200_engine_create_stack."""
+        dev = weights["embed"].device
+        if dev.type != "cuda":
+            raise B200Error("DecodeEngine: weights must be on a CUDA device (no CPU path)")
+        self.device = dev
+        self._w = weights
+        self._rope = None
+        self.local_vocab = spec.vocab
+        mdt = weights["embed"].dtype
+        if mdt not in (torch.bfloat16, torch.float32):
+            raise B200Error("DecodeEngine: stack matrices must be bf16 or fp32")
+        self.dtype = mdt
+
+        def ptr(name, dt):
+            t = weights.get(name)
+            if t is None:
+                return None
+            if t.dtype != dt or not t.is_contiguous() or t.device != dev:
+                raise B200Error(f"DecodeEngine: {name} must be a contiguous {dt} tensor on {dev}")
+            return t.data_ptr()
+
+        acts = {"gelu_tanh": 0, "silu": 1}
+        arr = (StackLayer * len(spec.layers))()
+        for i, L in enumerate(spec.layers):
+            a, lay, p = L.attn, spec.layout(i), f"l{i}."
+            side = spec.side_dim > 0
+            arr[i] = StackLayer(AttnDesc(a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window, a.keep_first,
+                                         int(a.out_gate)),
+                                L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate,
+                                lay.off_up, lay.n_in, lay.off_act, lay.k_out,
+                                ptr(p + "norm", torch.float32), ptr(p + "w_in", mdt), ptr(p + "b_in", torch.float32),
+                                ptr(p + "w_out", mdt), i * spec.side_dim,
+                                ptr(p + "side_gate", mdt) if side else None, ptr(p + "side_proj", mdt) if side else None,
+                                ptr(p + "side_norm", torch.float32) if side else None)
+        runs = spec.runs()
+        run_layer = (C.c_int32 * len(runs))(*[r[0] for r in runs])
+        run_mix = (C.c_int32 * len(runs))(*[int(r[1]) for r in runs])
+        desc = StackDesc(1 if mdt == torch.float32 else 0, 0, spec.width, spec.vocab, len(spec.layers), len(runs),
+                         run_layer, run_mix, spec.embed_scale, spec.residual_mult, spec.norm_eps, spec.norm_offset,
+                         spec.side_dim, spec.side_dim * len(spec.layers), spec.max_ctx, spec.max_slots,
+                         ptr("embed", mdt), ptr("mix_in", mdt), ptr("side_table", mdt), ptr("final_norm", torch.float32),
+                         ptr("head", mdt), arr)
+        h = C.c_void_p()
+        with torch.cuda.device(dev):
+            check(lib().b200_engine_create_stack(C.byref(desc), C.byref(h)), "b200_engine_create_stack")
+        self._h = h
+        self.slots = SequenceSlots(spec.max_slots)
+
+    # --------------------------------------------------------------------------------- ragged steps (stack engines)
+    def step(self, entries, greedy: bool = False) -> torch.Tensor:
+        """One ragged step.  `entries`: list of (slot, tokens, want) — `tokens` the sequence's next token ids, `want`
+        the places among them whose logits are returned.  → fp32 [Σ len(want), vocab] on the device, in the order of
+        the entries and of their `want`.  greedy: the last token of every entry also chooses that slot's next token, and
+        the entries become the batch `decode` continues."""
+        if not self.is_stack:
+            raise B200Error("DecodeEngine.step: ragged steps need a layer-stack model")
+        n = len(entries)
+        slots = (C.c_int32 * n)(*[int(e[0]) for e in entries])
+        counts = (C.c_int32 * n)(*[len(e[1]) for e in entries])
+        flat = [int(t) for e in entries for t in e[1]]
+        ids = (C.c_int64 * max(1, len(flat)))(*flat)
+        want, base = [], 0
+        for e in entries:
+            for k in e[2]:
+                if not 0 <= int(k) < len(e[1]):
+                    raise B200Error(f"DecodeEngine.step: wanted place {k} outside the entry's {len(e[1])} tokens")
+                want.append(base + int(k))
+            base += len(e[1])
+        wa = (C.c_int32 * max(1, len(want)))(*want)
+        out = torch.empty(len(want), self.spec.vocab, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            check(lib().b200_engine_step(self._h, n, slots, counts, ids, len(want), wa,
+                                         out.data_ptr() if want else None, int(greedy), self._stream()), "b200_engine_step")
+        if greedy:
+            self._batch = n
+        return out
+
+    def release(self, slot: int) -> None:
+        """The sequence in `slot` is over: position back to 0, the slot leaves the active batch."""
+        check(lib().b200_engine_slot_reset(self._h, int(slot), self._stream()), "b200_engine_slot_reset")
+
+    def slot_position(self, slot: int) -> int:
+        return int(lib().b200_engine_slot_position(self._h, int(slot)))
+
+    def generate_ragged(self, prompts, max_new_tokens: int) -> List[List[int]]:
+        """Greedy generation for prompts of unequal length WITHOUT padding (stack engines): one ragged prefill step,
+        then max_new_tokens - 1 batched decode steps on the device; sequence i lives in slot i."""
+        if max_new_tokens < 1 or not prompts or len(prompts) > self.spec.max_slots:
+            raise B200Error("generate_ragged: 1 … max_slots prompts and at least one new token")
+        self.reset_cache()
+        self.step([(i, list(p), []) for i, p in enumerate(prompts)], greedy=True)
+        first = torch.empty(len(prompts), 1, dtype=torch.int64, device=self.device)
+        check(lib().b200_engine_last_token(self._h, first.data_ptr(), self._stream()), "b200_engine_last_token")
+        rest = self.decode(max_new_tokens - 1).view(max_new_tokens - 1, -1).t()
+        return torch.cat([first, rest], dim=1).cpu().tolist()
 
     @staticmethod
     def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -146,8 +283,9 @@ class DecodeEngine:
     def forward(self, ids: torch.Tensor, all_positions: bool = False) -> torch.Tensor:
         """ids [1, S] int64 on the device → logits [1, S, V] (all_positions) or [1, 1, V] (last position) bf16.
         (Tensor-parallel engines return this rank's vocabulary shard, V / world columns.)"""
-        if ids.dim() != 2 or not 1 <= ids.shape[0] <= 8:
-            raise B200Error("DecodeEngine.forward: ids must be [B, S] with 1 ≤ B ≤ 8 (sequences at the same position)")
+        max_b = self.spec.max_slots if self.is_stack else 8
+        if ids.dim() != 2 or not 1 <= ids.shape[0] <= max_b:
+            raise B200Error(f"DecodeEngine.forward: ids must be [B, S] with 1 ≤ B ≤ {max_b} (sequences at the same position)")
         if ids.dtype != torch.int64 or not ids.is_cuda:
             raise B200Error("DecodeEngine.forward: ids must be int64 on the device (reference: FuncNNLayer.h:205)")
         ids = ids.contiguous()
@@ -184,6 +322,8 @@ class DecodeEngine:
         reference, the pad positions are attended — its mask is a TODO, GPTEngine.cpp:95).  → CPU int64 [B, new]."""
         if isinstance(prompts, (list, tuple)) and len(prompts) and not torch.is_tensor(prompts[0]) \
                 and len({len(p) for p in prompts}) > 1:
+            if self.is_stack:   # slots have their own positions: no padding, nothing attends a pad
+                return torch.tensor(self.generate_ragged(prompts, max_new_tokens), dtype=torch.int64)
             prompts, _ = align_prompts(prompts, self.spec.max_ctx, pad_token)
         prompts = torch.as_tensor(prompts, dtype=torch.int64)
         if prompts.dim() != 2 or prompts.shape[0] < 1:

@@ -322,3 +322,79 @@ def load_checkpoint(model_dir: str | Path, device: str | torch.device = "cuda", 
         return spec, w, {"bytes": cp.bytes, "unexpected": unexpected, "files": len(ck.files)}
     finally:
         ck.close()
+
+
+# ------------------------------------------------------------------------------------------------ layer-stack models
+def read_config(model_dir: str | Path) -> dict:
+    p = Path(model_dir)
+    p = p / "config.json" if p.is_dir() else p
+    try:
+        return json.loads(p.read_text())
+    except Exception as e:
+        raise LoaderError(f"Failed to load model config: {p}: {e}")
+
+
+def is_stack_model(model_dir: str | Path) -> bool:
+    """True when config.json names an architecture of the layer-stack registry (models.ARCHITECTURES)."""
+    return read_config(model_dir).get("architecture") in models.ARCHITECTURES
+
+
+def load_stack_config(model_dir: str | Path, max_ctx: Optional[int] = None,
+                      max_slots: Optional[int] = None) -> models.StackSpec:
+    doc = read_config(model_dir)
+    arch = doc.get("architecture")
+    if arch not in models.ARCHITECTURES:
+        raise LoaderError(f"Unsupported architecture: {arch!r} (layer-stack registry: {', '.join(models.ARCHITECTURES)})")
+    try:
+        spec = models.ARCHITECTURES[arch](doc)
+    except (KeyError, TypeError, ValueError) as e:
+        raise LoaderError(f"config.json: {type(e).__name__}: {e}")
+    if max_ctx is not None or max_slots is not None:
+        spec = spec.with_ctx(max_ctx if max_ctx is not None else spec.max_ctx, max_slots)
+    return spec
+
+
+_ST_DTYPES = {"BF16": (np.uint16, torch.bfloat16), "F32": (np.float32, torch.float32), "I32": (np.int32, torch.int32),
+              "F16": (np.float16, torch.float16)}
+
+
+def load_stack_checkpoint(model_dir: str | Path, device: str | torch.device = "cuda",
+                          dtype: torch.dtype = torch.bfloat16, max_ctx: Optional[int] = None,
+                          max_slots: Optional[int] = None) -> Tuple[models.StackSpec, Dict[str, torch.Tensor]]:
+    """config.json + model.safetensors of a layer-stack model → (spec, weights in the engine's layout on `device`).
+    Strict like the Llama-family load: every tensor the design names must be there with its shape."""
+    spec = load_stack_config(model_dir, max_ctx, max_slots)
+    f = SafeTensorsFile(Path(model_dir) / "model.safetensors")
+    named: Dict[str, torch.Tensor] = {}
+    for name, shape in models.kozusun_tensor_shapes(spec).items():
+        info = f.header.get(name)
+        if info is None:
+            raise LoaderError(f"missing tensor: {name}")
+        if tuple(info.get("shape", ())) != tuple(shape):
+            raise LoaderError(f"shape not equal for tensor: {name} (file {info.get('shape')}, model {list(shape)})")
+        if info.get("dtype") not in _ST_DTYPES:
+            raise LoaderError(f"dtype {info.get('dtype')!r} of tensor {name} is not read here")
+        np_dt, t_dt = _ST_DTYPES[info["dtype"]]
+        start, end = info["data_offsets"]
+        n = int(np.prod(shape)) if len(shape) else 1
+        if end - start != n * np.dtype(np_dt).itemsize or f._base + end > len(f._mm):
+            raise LoaderError(f"size not equal for tensor: {name}")
+        a = np.frombuffer(f._mm, dtype=np_dt, count=n, offset=f._base + start).reshape(shape).copy()
+        t = torch.from_numpy(a)
+        named[name] = t.view(torch.bfloat16) if t_dt == torch.bfloat16 else t
+    w = models.pack_stack_weights(spec, named, device=device, dtype=dtype)
+    del named
+    f.close()
+    return spec, w
+
+
+def load_model(model_dir: str | Path, device: str | torch.device = "cuda", dtype: torch.dtype = torch.bfloat16,
+               max_ctx: Optional[int] = None, max_slots: Optional[int] = None):
+    """Pick the model class by config.json and load it: (spec, weights) for engine.DecodeEngine.  "architecture" names a
+    layer-stack design, "model_type" a Llama-family checkpoint (bf16 only)."""
+    if is_stack_model(model_dir):
+        return load_stack_checkpoint(model_dir, device, dtype, max_ctx, max_slots)
+    if dtype != torch.bfloat16:
+        raise LoaderError("the Llama-family decode path is bf16 only")
+    spec, w, _ = load_checkpoint(model_dir, device, max_ctx=max_ctx)
+    return spec, w

@@ -11,7 +11,7 @@ import json
 import struct
 from dataclasses import dataclass, replace
 from pathlib import Path
-from typing import Dict, Optional
+from typing import Callable, Dict, List, Optional, Tuple
 
 import numpy as np
 import torch
@@ -177,6 +177,245 @@ def rope_table(spec: ModelSpec) -> torch.Tensor:
     tab = np.empty((spec.max_ctx, hd, 2), dtype=np.float32)
     tab[:, :half, 0], tab[:, :half, 1], tab[:, half:, 0], tab[:, half:, 1] = c, s, c, s
     return torch.from_numpy(tab)
+
+
+# ------------------------------------------------------------------------------------------------ layer-stack models
+# Models whose wiring is data: a list of layers (attention mixer + optional gated feed-forward + optional token-table
+# side input), optionally with a looped span.  The engine runs them through b200_engine_create_stack; what follows is
+# the host-side description, the registry that picks a description from config.json, and the weight layout.
+@dataclass(frozen=True)
+class AttnSpec:
+    heads: int
+    kv_heads: int
+    dim: int                 # per-head query/key size
+    vdim: int                # per-head value size
+    scale: float             # score = (q·k)·scale
+    window: int = 0          # key j visible from i when j <= i and i - j < window; 0 = every earlier key
+    keep_first: int = 0      # keys j < keep_first stay visible whatever the window
+    out_gate: bool = True    # head output × sigmoid(gate logit)
+    bias: bool = True        # q/k/v projections carry a bias
+
+    def visible(self, i: int, j: int) -> bool:
+        return j <= i and (self.window <= 0 or i - j < self.window or j < self.keep_first)
+
+
+@dataclass(frozen=True)
+class StackLayerSpec:
+    attn: AttnSpec
+    ff: int = 0                      # feed-forward width, 0 = none
+    ff_act: str = "gelu_tanh"        # gelu_tanh | silu
+
+
+@dataclass(frozen=True)
+class StackLayout:
+    """Rows of the merged in-projection and columns of the merged out-projection of one layer (segments start on
+    multiples of 8 so that vector loads and the tensor-core paths see aligned pieces; padding rows / columns are zero)."""
+    off_q: int
+    off_k: int
+    off_v: int
+    off_g: int
+    off_gate: int
+    off_up: int
+    n_in: int
+    off_act: int
+    k_out: int
+
+
+def _up8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+@dataclass(frozen=True)
+class StackSpec:
+    name: str
+    architecture: str
+    width: int
+    vocab: int
+    layers: Tuple[StackLayerSpec, ...]
+    loop_start: int = 0              # layers loop_start … loop_stop-1 run loop_times times in a row (own cache per pass),
+    loop_stop: int = 0               # every pass starting with x <- mix_in·[x; x0]; loop_times == 0: no loop
+    loop_times: int = 0
+    embed_scale: float = 1.0
+    residual_mult: float = 1.0
+    norm_eps: float = 1e-5
+    norm_offset: float = 0.0         # block / final norms multiply by (norm_offset + w)
+    side_dim: int = 0                # columns of the per-layer token table, 0 = none
+    max_ctx: int = 4096              # cache rows per slot
+    max_slots: int = 8               # sequences the engine holds at a time
+
+    def runs(self) -> List[Tuple[int, bool]]:
+        """(layer, mix the embedding in first) for every layer run, in execution order."""
+        n = len(self.layers)
+        if self.loop_times <= 0:
+            return [(i, False) for i in range(n)]
+        out = [(i, False) for i in range(self.loop_start)]
+        for _ in range(self.loop_times):
+            out += [(i, i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+        return out + [(i, False) for i in range(self.loop_stop, n)]
+
+    def layout(self, i: int) -> StackLayout:
+        L, a = self.layers[i], self.layers[i].attn
+        off_q = 0
+        off_k = off_q + _up8(a.heads * a.dim)
+        off_v = off_k + _up8(a.kv_heads * a.dim)
+        off_g = off_v + _up8(a.kv_heads * a.vdim)
+        off_gate = off_g + (_up8(a.heads) if a.out_gate else 0)
+        off_up = off_gate + _up8(L.ff)
+        n_in = off_up + _up8(L.ff)
+        off_act = _up8(a.heads * a.vdim)
+        return StackLayout(off_q, off_k, off_v, off_g, off_gate, off_up, n_in, off_act, off_act + _up8(L.ff))
+
+    def with_ctx(self, max_ctx: int, max_slots: Optional[int] = None) -> "StackSpec":
+        return replace(self, max_ctx=int(max_ctx), max_slots=int(max_slots if max_slots is not None else self.max_slots))
+
+    def weight_params(self) -> int:
+        """Matrix parameters one decode step reads (every run of a looped layer reads its layer again)."""
+        n = self.vocab * self.width
+        for i, mix in self.runs():
+            L, a = self.layers[i], self.layers[i].attn
+            n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.heads if a.out_gate else 0) + 2 * L.ff)
+            n += self.width * (a.heads * a.vdim + L.ff) + 2 * self.side_dim * self.width
+            n += 2 * self.width * self.width if mix else 0
+        return n
+
+
+def kozusun_from_config(doc: dict, name: str = "Kozusun") -> StackSpec:
+    """config.json of the Kozusun design → StackSpec.  Kozusun: parallel blocks (one zero-centred RMS norm feeds a gated
+    sliding-window attention with kept first tokens and a tanh-GELU gated feed-forward), a looped span of layers that
+    re-reads [x; x0] at the start of every pass, a gated per-layer token table added through a weighted RMS norm, scaled
+    embedding and residual."""
+    layers = []
+    for i, lc in enumerate(doc["layers"]):
+        if lc.get("type") != "attention":
+            raise ValueError(f"Kozusun: layer {i}: mixer type {lc.get('type')!r} is not part of the design")
+        m = lc["mixer"]
+        mask = m.get("mask") or {}
+        attn = AttnSpec(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                        scale=float(m["scale"]), window=int(mask.get("size", 0)), keep_first=int(mask.get("keep_first", 0)),
+                        out_gate=True, bias=True)
+        mlp = lc.get("mlp")
+        if mlp is not None and mlp.get("kind") != "dense":
+            raise ValueError(f"Kozusun: layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of the design")
+        layers.append(StackLayerSpec(attn=attn, ff=int(mlp["ff"]) if mlp is not None else 0, ff_act="gelu_tanh"))
+    loop = doc.get("loop") or {}
+    side = doc.get("token_side") or {}
+    spec = StackSpec(name=name, architecture="Kozusun", width=int(doc["width"]), vocab=int(doc["vocab"]),
+                     layers=tuple(layers), loop_start=int(loop.get("start", 0)), loop_stop=int(loop.get("stop", 0)),
+                     loop_times=int(loop.get("times", 0)), embed_scale=float(doc["embedding"]["scale"]),
+                     residual_mult=float(doc["residual_mult"]), norm_eps=float(doc["norm"]["eps"]), norm_offset=1.0,
+                     side_dim=int(side.get("dim", 0)))
+    if spec.loop_times > 0 and not 0 <= spec.loop_start < spec.loop_stop <= len(layers):
+        raise ValueError(f"Kozusun: loop {spec.loop_start}..{spec.loop_stop} does not fit {len(layers)} layers")
+    return spec
+
+
+# config.json "architecture" → reader.  (The Llama-family checkpoints are told apart by "model_type": loader.py.)
+ARCHITECTURES: Dict[str, Callable[[dict], StackSpec]] = {"Kozusun": kozusun_from_config}
+
+
+def kozusun_config(spec: StackSpec) -> dict:
+    """The config.json a Kozusun StackSpec is read from (inverse of kozusun_from_config)."""
+    doc = {"architecture": "Kozusun", "embedding": {"scale": spec.embed_scale}, "layers": [],
+           "norm": {"eps": spec.norm_eps}, "residual_mult": spec.residual_mult, "vocab": spec.vocab, "width": spec.width}
+    for L in spec.layers:
+        a = L.attn
+        doc["layers"].append({"type": "attention",
+                              "mixer": {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "vdim": a.vdim,
+                                        "scale": a.scale, "mask": {"keep_first": a.keep_first, "size": a.window}},
+                              "mlp": {"ff": L.ff, "kind": "dense"} if L.ff > 0 else None})
+    if spec.loop_times > 0:
+        doc["loop"] = {"start": spec.loop_start, "stop": spec.loop_stop, "times": spec.loop_times}
+    if spec.side_dim > 0:
+        doc["token_side"] = {"dim": spec.side_dim}
+    return doc
+
+
+def kozusun_tensor_shapes(spec: StackSpec) -> Dict[str, Tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a Kozusun model (Linear weights are [out, in])."""
+    W, out = spec.width, {}
+    out["embed"] = (spec.vocab, W)
+    if spec.loop_times > 0:
+        out["loop.in"] = (W, 2 * W)
+    if spec.side_dim > 0:
+        out["side.embed"] = (spec.vocab, spec.side_dim * len(spec.layers))
+    for i, L in enumerate(spec.layers):
+        a, p = L.attn, f"l{i}."
+        out[p + "norm1"] = (W,)
+        for nm, rows in (("q", a.heads * a.dim), ("k", a.kv_heads * a.dim), ("v", a.kv_heads * a.vdim)):
+            out[p + "mix." + nm] = (rows, W)
+            out[p + "mix." + nm + ".b"] = (rows,)
+        out[p + "mix.g"] = (a.heads, W)
+        out[p + "mix.o"] = (W, a.heads * a.vdim)
+        if L.ff > 0:
+            out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = (L.ff, W), (L.ff, W), (W, L.ff)
+        if spec.side_dim > 0:
+            out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = (spec.side_dim, W), (W, spec.side_dim), (W,)
+    out["final.norm"] = (W,)
+    out["head"] = (spec.vocab, W)
+    return out
+
+
+def synth_kozusun_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic Kozusun checkpoint (bf16, checkpoint names): matrices N(0, std·√(256/in)), vectors N(0, 0.1)."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in kozusun_tensor_shapes(spec).items():
+        if len(shape) == 1:
+            t = torch.randn(shape, generator=g) * 0.1
+            if name.endswith("side.norm"):
+                t = t + 1.0
+        else:
+            t = torch.randn(shape, generator=g) * (std * (256.0 / shape[1]) ** 0.5)
+        w[name] = t.to(torch.bfloat16)
+    return w
+
+
+def pack_stack_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
+                       dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Checkpoint tensors (Kozusun names) → the engine's layout on `device`: per layer w_in = [q | k | v | g | gate | up]
+    (rows, segments on multiples of 8, zero padding), b_in (fp32, zero where a segment has no bias), w_out = [o | down]
+    (columns), vectors in fp32; matrices in `dtype` (bf16 values are exact in fp32)."""
+    W = spec.width
+    out: Dict[str, torch.Tensor] = {}
+
+    def mat(t):
+        return t.to(dtype).contiguous().to(device)
+
+    def vec(t):
+        return t.to(torch.float32).contiguous().to(device)
+
+    out["embed"] = mat(named["embed"])
+    out["head"] = mat(named["head"])
+    out["final_norm"] = vec(named["final.norm"])
+    if spec.loop_times > 0:
+        out["mix_in"] = mat(named["loop.in"])
+    if spec.side_dim > 0:
+        out["side_table"] = mat(named["side.embed"])
+    for i, L in enumerate(spec.layers):
+        a, lay, p = L.attn, spec.layout(i), f"l{i}."
+        w_in = torch.zeros(lay.n_in, W, dtype=dtype)
+        b_in = torch.zeros(lay.n_in, dtype=torch.float32)
+        segs = [("q", lay.off_q), ("k", lay.off_k), ("v", lay.off_v)]
+        for nm, off in segs:
+            t = named[p + "mix." + nm]
+            w_in[off:off + t.shape[0]] = t.to(dtype)
+            if a.bias:
+                b_in[off:off + t.shape[0]] = named[p + "mix." + nm + ".b"].to(torch.float32)
+        if a.out_gate:
+            w_in[lay.off_g:lay.off_g + a.heads] = named[p + "mix.g"].to(dtype)
+        w_out = torch.zeros(W, lay.k_out, dtype=dtype)
+        w_out[:, :a.heads * a.vdim] = named[p + "mix.o"].to(dtype)
+        if L.ff > 0:
+            w_in[lay.off_gate:lay.off_gate + L.ff] = named[p + "mlp.gate"].to(dtype)
+            w_in[lay.off_up:lay.off_up + L.ff] = named[p + "mlp.up"].to(dtype)
+            w_out[:, lay.off_act:lay.off_act + L.ff] = named[p + "mlp.down"].to(dtype)
+        out[p + "norm"] = vec(named[p + "norm1"])
+        out[p + "w_in"], out[p + "b_in"], out[p + "w_out"] = w_in.to(device), b_in.to(device), w_out.to(device)
+        if spec.side_dim > 0:
+            out[p + "side_gate"] = mat(named[p + "side.gate"])
+            out[p + "side_proj"] = mat(named[p + "side.proj"])
+            out[p + "side_norm"] = vec(named[p + "side.norm"])
+    return out
 
 
 # ------------------------------------------------------------------------------------------- checkpoint writer
