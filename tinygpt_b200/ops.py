@@ -195,3 +195,92 @@ def sample(logits: torch.Tensor, temperature: float, top_k: int = 0, top_p: floa
     check(lib().b200_sample_bf16(out.data_ptr(), logits.data_ptr(), logits.numel(), float(temperature), int(top_k),
                                  float(top_p), float(min_p), float(u), ws.data_ptr(), _stream()), "b200_sample_bf16")
     return out
+
+
+# ------------------------------------------------------------------------------- mechanisms of the layer-stack engine
+# T = bf16 or fp32 storage (taken from the tensors); norms, softmax, gates and accumulation are fp32 in both.
+def _sdt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 0
+    if t.dtype == torch.float32:
+        return 1
+    raise B200Error(f"stack op: dtype {t.dtype} (bf16 or fp32)")
+
+
+def _tdt(code_or_dtype) -> torch.dtype:
+    return code_or_dtype if isinstance(code_or_dtype, torch.dtype) else (torch.float32 if code_or_dtype else torch.bfloat16)
+
+
+def stack_rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, offset: float = 0.0,
+                  out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out_dtype( x·rsqrt(mean(x²) + eps)·(offset + w) ) for fp32 x [rows, dim] and fp32 w [dim]."""
+    x, w = _chk(x, "stack_rmsnorm x", torch.float32), _chk(w, "stack_rmsnorm w", torch.float32)
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(lib().b200_stack_rmsnorm(y.data_ptr(), x.data_ptr(), w.data_ptr(), x.numel() // x.shape[-1], x.shape[-1],
+                                   float(eps), float(offset), _sdt(y), _stream()), "b200_stack_rmsnorm")
+    return y
+
+
+def stack_linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a [M, K] · weight [N, K]ᵀ (+ fp32 bias [N]) with fp32 accumulation, any sizes; a, weight and the result share T."""
+    a, weight = _chk(a, "stack_linear a", a.dtype), _chk(weight, "stack_linear weight", a.dtype)
+    if bias is not None:
+        bias = _chk(bias, "stack_linear bias", torch.float32)
+    M, K = a.shape
+    N = weight.shape[0]
+    if weight.shape[1] != K:
+        raise B200Error("stack_linear: inner sizes differ")
+    c = torch.empty(M, N, dtype=a.dtype, device=a.device)
+    check(lib().b200_stack_linear(c.data_ptr(), a.data_ptr(), weight.data_ptr(), _ptr(bias), M, N, K, _sdt(a), _stream()),
+          "b200_stack_linear")
+    return c
+
+
+def _attn_desc(heads, kv_heads, dim, vdim, scale, window, keep_first, out_gate):
+    from ._lib import AttnDesc
+    return AttnDesc(int(heads), int(kv_heads), int(dim), int(vdim), float(scale), int(window), int(keep_first),
+                    int(bool(out_gate)))
+
+
+def stack_kv_store(kcache: torch.Tensor, vcache: torch.Tensor, proj: torch.Tensor, off_k: int, off_v: int,
+                   slot: torch.Tensor, pos: torch.Tensor, *, heads, kv_heads, dim, vdim) -> None:
+    """Rows pos[t] of slot[t]'s cache ← the k / v segments of proj[t].  kcache [slots, ctx, kv_heads·dim], vcache
+    [slots, ctx, kv_heads·vdim]; slot, pos int32 [n_tok]."""
+    import ctypes as C
+    d = _attn_desc(heads, kv_heads, dim, vdim, 1.0, 0, 0, 0)
+    check(lib().b200_stack_kv_store(kcache.data_ptr(), vcache.data_ptr(), kcache.stride(0), vcache.stride(0),
+                                    proj.data_ptr(), proj.stride(0), off_k, off_v, slot.data_ptr(), pos.data_ptr(),
+                                    proj.shape[0], C.byref(d), _sdt(proj), _stream()), "b200_stack_kv_store")
+
+
+def stack_attention(proj: torch.Tensor, off_q: int, off_g: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                    slot: torch.Tensor, pos: torch.Tensor, *, heads, kv_heads, dim, vdim, scale, window=0, keep_first=0,
+                    out_gate=False) -> torch.Tensor:
+    """Windowed attention of n_tok query rows (q at columns off_q of proj, gate logits at off_g) over the slots' caches →
+    [n_tok, heads·vdim]."""
+    import ctypes as C
+    d = _attn_desc(heads, kv_heads, dim, vdim, scale, window, keep_first, out_gate)
+    out = torch.empty(proj.shape[0], heads * vdim, dtype=proj.dtype, device=proj.device)
+    check(lib().b200_stack_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), off_q, off_g,
+                                     kcache.data_ptr(), vcache.data_ptr(), kcache.stride(0), vcache.stride(0),
+                                     slot.data_ptr(), pos.data_ptr(), proj.shape[0], C.byref(d), _sdt(proj), _stream()),
+          "b200_stack_attention")
+    return out
+
+
+def stack_act_mul(g: torch.Tensor, u: torch.Tensor, act: str = "gelu_tanh") -> torch.Tensor:
+    """T( act(g)·u ) elementwise over [rows, n] (row strides may differ from n: column slices of one projection)."""
+    if g.shape != u.shape or g.stride(0) != u.stride(0) or g.stride(1) != 1 or u.stride(1) != 1 or g.dtype != u.dtype:
+        raise B200Error("stack_act_mul: g and u must be equally shaped column slices of one row-major matrix")
+    y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
+    check(lib().b200_stack_act_mul(y.data_ptr(), y.stride(0), g.data_ptr(), u.data_ptr(), g.stride(0), g.shape[0],
+                                   g.shape[1], {"gelu_tanh": 0, "silu": 1}[act], _sdt(g), _stream()), "b200_stack_act_mul")
+    return y
+
+
+def stack_rms_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, mult: float) -> torch.Tensor:
+    """x += mult · y·rsqrt(mean(y²) + eps)·w, in place on fp32 x [rows, dim]; returns x."""
+    x, y, w = (_chk(t, "stack_rms_add", torch.float32) for t in (x, y, w))
+    check(lib().b200_stack_rms_add(x.data_ptr(), y.data_ptr(), w.data_ptr(), x.numel() // x.shape[-1], x.shape[-1],
+                                   float(eps), float(mult), _stream()), "b200_stack_rms_add")
+    return x
