@@ -57,7 +57,21 @@ struct StackEngine {
   __nv_bfloat16* logits_bf = nullptr;
   int32_t *m_tok = nullptr, *m_slot = nullptr, *m_pos = nullptr, *m_want = nullptr, *m_upd = nullptr;
   int n_in_max = 0, k_out_max = 0;
+  // bf16 engines: the big products leave the general kernel where their shapes allow — the weight-streaming GEMV
+  // (gemv.cu / gemv_batch.cu) for steps of up to kMaxBatch rows, the tcgen05 GEMM (gemm.cu) for steps of kGemmRows and
+  // more rows; B200_STACK_PLAIN=1 keeps everything on the general kernels
+  bool fast = false;
+  int num_sms = 148;
+  struct Plans {
+    GemvPlan in{}, out{};
+    bool ok_in = false, ok_out = false;
+  };
+  std::vector<Plans> plans;
+  GemvPlan p_mix{}, p_head{};
+  bool ok_mix = false, ok_head = false;
+  __nv_bfloat16* cat = nullptr;   // bf16 [x | x0] rows for the mix-in product
 };
+constexpr int kGemmRows = 32;
 
 namespace {
 
@@ -125,6 +139,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_hn = take((size_t)rows * W * s->esz), o_lg = take((size_t)rows * d.vocab * 4);
   const size_t o_lb = take((size_t)rows * d.vocab * 2);
   const size_t o_meta = take((3 * T + rows + 2 * (size_t)d.max_slots) * 4);
+  const size_t o_cat = take(d.mix_in != nullptr && s->dtype == B200_BF16 ? T * 2 * W * 2 : 0);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->ws_tok = tok;
@@ -145,7 +160,103 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->m_pos = s->m_slot + T;
   s->m_want = s->m_pos + T;
   s->m_upd = s->m_want + rows;
+  s->cat = (__nv_bfloat16*)(s->ws + o_cat);
   return B200_OK;
+}
+
+static inline bool gemm_shape_ok(int64_t N, int64_t K) { return N % 8 == 0 && K % 8 == 0 && K >= 64; }
+
+// proj = h·w_inᵀ + b_in
+static int stack_product_in(StackEngine* s, int li, int n_tok, cudaStream_t st) {
+  const b200_stack_layer& L = s->layers[li];
+  const int W = s->d.width;
+  int rc;
+  if (s->fast && n_tok <= kMaxBatch && s->plans[li].ok_in) {
+    GemvPlan pl = s->plans[li].in;
+    pl.p.x = (const __nv_bfloat16*)s->h;
+    pl.p.y = (__nv_bfloat16*)s->proj;
+    pl.p.fbias = L.b_in;
+    if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
+    return gemv_launch(pl, st, false);
+  }
+  if (s->fast && n_tok >= kGemmRows && gemm_shape_ok(L.n_in, W)) {
+    if ((rc = launch_gemm_bf16(s->proj, s->h, L.w_in, n_tok, L.n_in, W, st)) != B200_OK) return rc;
+    return L.b_in ? launch_stack_bias_add((__nv_bfloat16*)s->proj, L.b_in, n_tok, L.n_in, st) : B200_OK;
+  }
+  StackGemm g;
+  g.a = s->h; g.lda = W; g.k1 = W;
+  g.w = L.w_in; g.bias = L.b_in; g.M = n_tok; g.N = L.n_in; g.K = W;
+  g.epi = SEPI_STORE; g.c = s->proj; g.ldc = L.n_in;
+  return launch_stack_gemm(g, s->dtype, st);
+}
+
+// x += m · mid·w_outᵀ
+static int stack_product_out(StackEngine* s, int li, float* x, int n_tok, cudaStream_t st) {
+  const b200_stack_layer& L = s->layers[li];
+  const int W = s->d.width;
+  int rc;
+  if (s->fast && n_tok <= kMaxBatch && s->plans[li].ok_out) {
+    GemvPlan pl = s->plans[li].out;
+    pl.p.x = (const __nv_bfloat16*)s->mid;
+    pl.p.yf = x;
+    pl.p.mult = s->d.residual_mult;
+    if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
+    return gemv_launch(pl, st, false);
+  }
+  if (s->fast && n_tok >= kGemmRows && gemm_shape_ok(W, L.k_out)) {   // h is free again: it holds the bf16 product
+    if ((rc = launch_gemm_bf16(s->h, s->mid, L.w_out, n_tok, W, L.k_out, st)) != B200_OK) return rc;
+    return launch_stack_axpy(x, (const __nv_bfloat16*)s->h, s->d.residual_mult, true, (int64_t)n_tok * W, st);
+  }
+  StackGemm g;
+  g.a = s->mid; g.lda = L.k_out; g.k1 = L.k_out;
+  g.w = L.w_out; g.M = n_tok; g.N = W; g.K = L.k_out;
+  g.epi = SEPI_RESIDUAL; g.c = x; g.ldc = W; g.mult = s->d.residual_mult;
+  return launch_stack_gemm(g, s->dtype, st);
+}
+
+// other = mix_in·[cur; x0]
+static int stack_product_mix(StackEngine* s, const float* cur, float* other, int n_tok, cudaStream_t st) {
+  const int W = s->d.width;
+  int rc;
+  const bool gemv = s->fast && n_tok <= kMaxBatch && s->ok_mix;
+  const bool gemm = s->fast && n_tok >= kGemmRows && gemm_shape_ok(W, 2 * W);
+  if (gemv || gemm) {
+    if ((rc = launch_stack_cat_cast(s->cat, cur, s->x0, gemv ? other : nullptr, n_tok, W, st)) != B200_OK) return rc;
+    if (gemv) {
+      GemvPlan pl = s->p_mix;
+      pl.p.x = s->cat;
+      pl.p.yf = other;
+      pl.p.mult = 1.f;
+      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
+      return gemv_launch(pl, st, false);
+    }
+    if ((rc = launch_gemm_bf16(s->h, s->cat, s->d.mix_in, n_tok, W, 2 * W, st)) != B200_OK) return rc;
+    return launch_stack_axpy(other, (const __nv_bfloat16*)s->h, 1.f, false, (int64_t)n_tok * W, st);
+  }
+  StackGemm g;
+  g.a = cur; g.a2 = s->x0; g.lda = g.lda2 = W; g.k1 = W; g.a_f32 = true;
+  g.w = s->d.mix_in; g.M = n_tok; g.N = W; g.K = 2 * W;
+  g.epi = SEPI_STORE_F32; g.c = other; g.ldc = W;
+  return launch_stack_gemm(g, s->dtype, st);
+}
+
+// logits (fp32) and logits_bf (bf16) = hn·headᵀ
+static int stack_product_head(StackEngine* s, int n_rows, cudaStream_t st) {
+  const b200_stack_desc& d = s->d;
+  int rc;
+  if (s->fast && n_rows <= kMaxBatch && s->ok_head) {
+    GemvPlan pl = s->p_head;
+    pl.p.x = (const __nv_bfloat16*)s->hn;
+    pl.p.y = s->logits_bf;
+    pl.p.yf = s->logits;
+    if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
+    return gemv_launch(pl, st, false);
+  }
+  StackGemm g;
+  g.a = s->hn; g.lda = d.width; g.k1 = d.width;
+  g.w = d.head; g.M = n_rows; g.N = d.vocab; g.K = d.width;
+  g.epi = SEPI_LOGITS; g.c = s->logits; g.ldc = d.vocab; g.c2 = s->logits_bf;
+  return launch_stack_gemm(g, s->dtype, st);
 }
 
 // One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
@@ -160,22 +271,12 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
   for (int r = 0; r < d.n_runs; ++r) {
     const b200_stack_layer& L = s->layers[s->run_layer[r]];
     if (s->run_mix[r]) {
-      StackGemm g;
-      g.a = cur; g.a2 = s->x0; g.lda = g.lda2 = W; g.k1 = W; g.a_f32 = true;
-      g.w = d.mix_in; g.M = n_tok; g.N = W; g.K = 2 * W;
-      g.epi = SEPI_STORE_F32; g.c = other; g.ldc = W;
-      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      if ((rc = stack_product_mix(s, cur, other, n_tok, st)) != B200_OK) return rc;
       std::swap(cur, other);
     }
     if ((rc = launch_stack_rmsnorm(s->h, cur, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, dt, st)) != B200_OK)
       return rc;
-    {
-      StackGemm g;
-      g.a = s->h; g.lda = W; g.k1 = W;
-      g.w = L.w_in; g.bias = L.b_in; g.M = n_tok; g.N = L.n_in; g.K = W;
-      g.epi = SEPI_STORE; g.c = s->proj; g.ldc = L.n_in;
-      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
-    }
+    if ((rc = stack_product_in(s, s->run_layer[r], n_tok, st)) != B200_OK) return rc;
     StackAttn a;
     a.a = L.attn;
     a.proj = s->proj; a.ld_proj = L.n_in;
@@ -196,13 +297,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
                                      p + (size_t)L.off_up * s->esz, L.n_in, n_tok, L.ff, L.ff_act, dt, st)) != B200_OK)
         return rc;
     }
-    {
-      StackGemm g;
-      g.a = s->mid; g.lda = L.k_out; g.k1 = L.k_out;
-      g.w = L.w_out; g.M = n_tok; g.N = W; g.K = L.k_out;
-      g.epi = SEPI_RESIDUAL; g.c = cur; g.ldc = W; g.mult = d.residual_mult;
-      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
-    }
+    if ((rc = stack_product_out(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
     if (L.side_gate != nullptr) {
       StackGemm g;
       g.a = cur; g.lda = W; g.k1 = W; g.a_f32 = true;
@@ -223,11 +318,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
     if ((rc = launch_stack_rmsnorm(s->hn, cur, d.final_norm, s->m_want, n_rows, W, d.norm_eps, d.norm_offset, dt, st)) !=
         B200_OK)
       return rc;
-    StackGemm g;
-    g.a = s->hn; g.lda = W; g.k1 = W;
-    g.w = d.head; g.M = n_rows; g.N = d.vocab; g.K = W;
-    g.epi = SEPI_LOGITS; g.c = s->logits; g.ldc = d.vocab; g.c2 = s->logits_bf;
-    if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+    if ((rc = stack_product_head(s, n_rows, st)) != B200_OK) return rc;
   }
   return B200_OK;
 }
@@ -517,6 +608,28 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
   }
   B200_CUDA(cudaDeviceSynchronize());   // weights may still be in flight on the loader's stream
+  {
+    int dev = 0;
+    B200_CUDA(cudaGetDevice(&dev));
+    B200_CUDA(cudaDeviceGetAttribute(&s->num_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  s->plans.resize(d.n_layers);
+  s->fast = d.dtype == B200_BF16 && !env_flag("B200_STACK_PLAIN", false);
+  if (s->fast) {
+    if ((rc = gemv_setup_attributes()) != B200_OK || (rc = gemv_batch_setup_attributes()) != B200_OK) return rc;
+    // a plan that cannot be made (k not a multiple of 8, an unaligned matrix) leaves that product on the general kernel
+    auto plan = [&](GemvPlan* pl, const void* w, int64_t n, int64_t k, int epi) {
+      if (k % 8 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
+      return gemv_make_plan(pl, w, n, n, k, 1, PRO_PLAIN, epi, s->num_sms) == B200_OK;
+    };
+    for (int l = 0; l < d.n_layers; ++l) {
+      const b200_stack_layer& L = s->layers[l];
+      s->plans[l].ok_in = plan(&s->plans[l].in, L.w_in, L.n_in, d.width, EPI_BIAS_F32);
+      s->plans[l].ok_out = plan(&s->plans[l].out, L.w_out, d.width, L.k_out, EPI_RESID_F32);
+    }
+    if (d.mix_in) s->ok_mix = plan(&s->p_mix, d.mix_in, d.width, 2 * (int64_t)d.width, EPI_RESID_F32);
+    s->ok_head = plan(&s->p_head, d.head, d.vocab, d.width, EPI_BIAS_F32);
+  }
   const size_t kb = align_up(s->k_slot * d.max_slots * s->esz, 256), vb = align_up(s->v_slot * d.max_slots * s->esz, 256);
   B200_CUDA(cudaMalloc((void**)&s->cache, kb + vb));
   s->kbase = s->cache;

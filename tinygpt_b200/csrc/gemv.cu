@@ -356,6 +356,12 @@ gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap)
         const float g = round_bf16(a0);
         const __nv_bfloat16 sg = f_to_bf16(g / (1.f + expf(-g)));
         p.y[row] = __hmul(sg, f_to_bf16(a1));
+      } else if constexpr (EPI == EPI_BIAS_F32) {
+        const float v = a0 + (p.fbias != nullptr ? p.fbias[row] : 0.f);
+        if (p.yf != nullptr) p.yf[row] = v;   // the unrounded value too (fp32 logits beside the sampler's bf16 copy)
+        p.y[row] = f_to_bf16(v);
+      } else if constexpr (EPI == EPI_RESID_F32) {
+        p.yf[row] += p.mult * a0;
       } else {  // EPI_TP_PUSH: one 8-byte {value, tag} store per rank, no fence needed
         const uint2 pk = make_uint2(__float_as_uint(a0), tp_tag);
         for (int q = 0; q < p.tp_world; ++q) st_volatile_u2(p.tp_push[q] + row, pk);
@@ -389,6 +395,8 @@ KernelFn pick_kernel(int nseg, int pro, int epi) {
   B200_PICK(PRO_PLAIN, EPI_RESIDUAL)
   B200_PICK(PRO_PLAIN, EPI_TP_PUSH)
   B200_PICK(PRO_RMSNORM, EPI_PLAIN)
+  B200_PICK(PRO_PLAIN, EPI_BIAS_F32)
+  B200_PICK(PRO_PLAIN, EPI_RESID_F32)
   B200_PICK(PRO_TP_RMSNORM, EPI_PLAIN)
 #undef B200_PICK
   return nullptr;
@@ -413,7 +421,7 @@ int gemv_setup_attributes() {
     for (int rpw : rpws)
       for (int nseg = 1; nseg <= 2; ++nseg)
         for (int pro = 0; pro < 3; ++pro)
-          for (int epi = 0; epi < 4; ++epi) {
+          for (int epi = 0; epi < kGemvEpiCount; ++epi) {
             KernelFn f = pick(rpw, nseg, pro, epi);
             if (!f) continue;
             cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem + 4096);

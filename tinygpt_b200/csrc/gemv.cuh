@@ -14,7 +14,11 @@ enum GemvPro : int { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_TP_RMSNORM = 2 };
 //   EPI_RESIDUAL  y = bf16(residual + bf16(acc))                        (o_proj / down_proj + DecoderLayer add)
 //   EPI_SILU_MUL  y = bf16(bf16(silu(bf16(acc_gate))) * bf16(acc_up))   (merged gate|up projection + SiLUMul)
 //   EPI_TP_PUSH   fp32 acc stored into every tensor-parallel peer's exchange window + arrival flag
-enum GemvEpi : int { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_TP_PUSH = 3 };
+//   EPI_BIAS_F32  y = bf16(acc + fbias)                                 (stack models: fp32 bias, one rounding)
+//   EPI_RESID_F32 yf += mult · acc                                      (stack models: fp32 residual stream)
+enum GemvEpi : int { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_TP_PUSH = 3, EPI_BIAS_F32 = 4,
+                     EPI_RESID_F32 = 5 };
+constexpr int kGemvEpiCount = 6;
 
 constexpr int kMaxTpWorld = 8;
 constexpr int kMaxBatch = 8;   // sequences one batched decode step serves (gemv_batch.cu: W streamed once for all of them)
@@ -38,6 +42,9 @@ struct GemvParams {
   const __nv_bfloat16* bias;      // [n] or null
   const __nv_bfloat16* residual;  // [n]; may alias y
   __nv_bfloat16* y;               // [n]
+  const float* fbias;             // EPI_BIAS_F32: [n] or null
+  float* yf;                      // EPI_RESID_F32: [n] fp32 stream the scaled row sums are added to
+  float mult;                     // EPI_RESID_F32
   // batched decode (gemv_batch.cu): `batch` sequences, x / residual / y of sequence b at b·stride elements
   int batch;                      // 0 or 1: the single-sequence kernels
   int x_stride, y_stride;         // = k, n (residual uses y_stride)

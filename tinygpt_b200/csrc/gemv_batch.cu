@@ -58,7 +58,9 @@ gemv_batch_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) 
   constexpr bool kHalfTile = kRowsStage == 8;       // rows 8-15 of the only tile do not exist: a1 = a3 = 0
   constexpr int kSliceK = KB * 32;                  // k-elements of a stage one warp owns
   static_assert(PRO == PRO_PLAIN || PRO == PRO_RMSNORM, "single-GPU prologues only");
-  static_assert(EPI == EPI_PLAIN || EPI == EPI_RESIDUAL || EPI == EPI_SILU_MUL, "single-GPU epilogues only");
+  static_assert(EPI == EPI_PLAIN || EPI == EPI_RESIDUAL || EPI == EPI_SILU_MUL || EPI == EPI_BIAS_F32 ||
+                    EPI == EPI_RESID_F32,
+                "single-GPU epilogues only");
 
   const int nb = p.batch;
   const int xstride = p.k_pad + kXPad;
@@ -299,6 +301,12 @@ gemv_batch_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) 
         y[row] = v;
       } else if constexpr (EPI == EPI_RESIDUAL) {
         y[row] = __hadd(res_v, f_to_bf16(a[0]));
+      } else if constexpr (EPI == EPI_BIAS_F32) {
+        const float v = a[0] + (p.fbias != nullptr ? p.fbias[row] : 0.f);
+        if (p.yf != nullptr) p.yf[(size_t)it_b * p.y_stride + row] = v;
+        y[row] = f_to_bf16(v);
+      } else if constexpr (EPI == EPI_RESID_F32) {
+        p.yf[(size_t)it_b * p.y_stride + row] += p.mult * a[0];
       } else {  // EPI_SILU_MUL
         const float gt = round_bf16(a[0]);
         const __nv_bfloat16 sg = f_to_bf16(gt / (1.f + expf(-gt)));
@@ -318,6 +326,8 @@ KernelFn pick_r(int nseg, int pro, int epi) {
   if (nseg == 2) return (pro == PRO_RMSNORM && epi == EPI_SILU_MUL) ? gemv_batch_kernel<RPW, 2, PRO_RMSNORM, EPI_SILU_MUL> : nullptr;
   if (pro == PRO_RMSNORM && epi == EPI_PLAIN) return gemv_batch_kernel<RPW, 1, PRO_RMSNORM, EPI_PLAIN>;
   if (pro == PRO_PLAIN && epi == EPI_RESIDUAL) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_RESIDUAL>;
+  if (pro == PRO_PLAIN && epi == EPI_BIAS_F32) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_BIAS_F32>;
+  if (pro == PRO_PLAIN && epi == EPI_RESID_F32) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_RESID_F32>;
   return nullptr;
 }
 KernelFn pick(int rpw, int nseg, int pro, int epi) {
@@ -346,7 +356,7 @@ int gemv_batch_setup_attributes() {
     for (int rpw : rpws)
       for (int nseg = 1; nseg <= 2; ++nseg)
         for (int pro = 0; pro < 2; ++pro)
-          for (int epi = 0; epi < 3; ++epi) {
+          for (int epi = 0; epi < kGemvEpiCount; ++epi) {
             KernelFn f = pick(rpw, nseg, pro, epi);
             if (!f) continue;
             cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem + 4096);
@@ -376,6 +386,7 @@ int gemv_batch_launch(const GemvPlan& plan, cudaStream_t stream, bool pdl) {
     p.x += (size_t)b0 * p.x_stride;
     p.y += (size_t)b0 * p.y_stride;
     if (p.residual) p.residual += (size_t)b0 * p.y_stride;
+    if (p.yf) p.yf += (size_t)b0 * p.y_stride;
     if (b0 + per < plan.batch) p.pos_inc = nullptr;       // the position advances once, after the last launch
     B200_CUDA(launch_pdl(f, dim3(plan.grid), dim3(kThreads), (size_t)plan.smem, stream, pdl, p, plan.tmap));
   }

@@ -48,6 +48,15 @@ int launch_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, in
 int launch_stack_embed(float* x, float* x0, const void* embed, const int32_t* tok, int64_t n_tok, int vocab, int width,
                        float scale, int dtype, cudaStream_t st);
 
+// ---- glue of the bf16 tensor-core / weight-streaming paths (engine_stack.cu picks them per product)
+// y[r, j] = bf16(float(y[r, j]) + b[j])
+int launch_stack_bias_add(__nv_bfloat16* y, const float* b, int64_t rows, int n, cudaStream_t st);
+// x[i] = (add ? x[i] : 0) + mult · float(t[i])
+int launch_stack_axpy(float* x, const __nv_bfloat16* t, float mult, bool add, int64_t total, cudaStream_t st);
+// cat[r, :] = bf16([a[r, :] | b[r, :]]) (each `width` wide); zero_or_null[r, :] = 0
+int launch_stack_cat_cast(__nv_bfloat16* cat, const float* a, const float* b, float* zero_or_null, int64_t rows, int width,
+                          cudaStream_t st);
+
 struct StackAttn {
   b200_attn_desc a{};
   const void* proj = nullptr;   // [n_tok, ld_proj] T: q at off_q (heads·dim), k at off_k, v at off_v, gate logits at off_g

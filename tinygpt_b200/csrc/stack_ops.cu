@@ -176,19 +176,22 @@ __global__ void __launch_bounds__(128) stack_kv_store_kernel(const StackAttn p) 
   for (int i = threadIdx.x; i < nv; i += blockDim.x) vd[i] = row[p.off_v + i];
 }
 
-// One warp per (token, query head).  The visible keys of a query at position i are the kept first rows
-// [0, min(keep_first, lo)) followed by the window [lo, i], lo = max(0, i − window + 1) (window 0: lo = 0).  The warp
-// walks that list 32 keys at a time: lane j scores key j (fp32 dot, times scale), the chunk joins an online softmax,
-// then the lanes turn to the value columns (lane + 32·r) and add the chunk's 32 weighted rows.
-template <typename T, int VR>
+// NW warps per (token, query head); NW = 1: four pairs per CTA (prompts: pairs abound), NW = 4: one pair per CTA, its keys
+// dealt to the warps 32 at a time and the partial softmaxes merged through shared memory (decode steps: few pairs, long
+// key lists).  The visible keys of a query at position i are the kept first rows [0, min(keep_first, lo)) followed by
+// the window [lo, i], lo = max(0, i − window + 1) (window 0: lo = 0).  A warp walks its share of that list 32 keys at a
+// time: lane j scores key j (fp32 dot, times scale; VEC: 16-byte loads of bf16 rows), the chunk joins an online softmax,
+// then the lanes turn to the value columns (lane + 32·r) and add the chunk's weighted rows.
+template <typename T, int VR, int NW, bool VEC>
 __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
-  extern __shared__ float qs_all[];
+  extern __shared__ float smem_f[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
+  const int wi = warp % NW;
+  const int64_t pair = (int64_t)blockIdx.x * (4 / NW) + warp / NW;
   const int t = (int)(pair / p.a.heads), h = (int)(pair % p.a.heads);
-  if (t >= p.n_tok) return;
+  if (t >= p.n_tok) return;   // NW = 4: the whole CTA leaves together
   const int dim = p.a.dim, vdim = p.a.vdim;
-  float* qs = qs_all + warp * dim;
+  float* qs = smem_f + warp * dim;
   const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
   for (int d = lane; d < dim; d += 32) qs[d] = ldf<T>(prow + p.off_q + h * dim + d);
   __syncwarp();
@@ -203,7 +206,7 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   float m = -INFINITY, l = 0.f, acc[VR];
 #pragma unroll
   for (int r = 0; r < VR; ++r) acc[r] = 0.f;
-  for (int c0 = 0; c0 < total; c0 += 32) {
+  for (int c0 = wi * 32; c0 < total; c0 += NW * 32) {
     const int idx = c0 + lane;
     const bool valid = idx < total;
     const int j = idx < na ? idx : lo + (idx - na);
@@ -211,7 +214,17 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     if (valid) {
       const T* kr = kb + (int64_t)j * krs;
       float dot = 0.f;
-      for (int d = 0; d < dim; ++d) dot = fmaf(qs[d], ldf<T>(kr + d), dot);
+      if constexpr (VEC) {
+        const uint4* k4 = reinterpret_cast<const uint4*>(kr);
+        for (int d8 = 0; d8 < (dim >> 3); ++d8) {
+          float kf[8];
+          unpack8(k4[d8], kf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) dot = fmaf(qs[d8 * 8 + e], kf[e], dot);
+        }
+      } else {
+        for (int d = 0; d < dim; ++d) dot = fmaf(qs[d], ldf<T>(kr + d), dot);
+      }
       s = dot * p.a.scale;
     }
     const float mn = fmaxf(m, warp_max(s));
@@ -233,6 +246,37 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     }
     m = mn;
   }
+  if constexpr (NW > 1) {
+    // merge the warps' partial softmaxes: scratch [NW][2 + vdim] behind the four query vectors
+    float* sc = smem_f + 4 * dim;
+    float* mine = sc + wi * (2 + vdim);
+    if (lane == 0) {
+      mine[0] = m;
+      mine[1] = l;
+    }
+#pragma unroll
+    for (int r = 0; r < VR; ++r) {
+      const int d = lane + 32 * r;
+      if (d < vdim) mine[2 + d] = acc[r];
+    }
+    __syncthreads();
+    if (wi != 0) return;
+    float mt = -INFINITY;
+    for (int w = 0; w < NW; ++w) mt = fmaxf(mt, sc[w * (2 + vdim)]);
+    l = 0.f;
+#pragma unroll
+    for (int r = 0; r < VR; ++r) acc[r] = 0.f;
+    for (int w = 0; w < NW; ++w) {
+      const float* o = sc + w * (2 + vdim);
+      const float f = o[0] == -INFINITY ? 0.f : expf(o[0] - mt);
+      l += o[1] * f;
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < vdim) acc[r] += o[2 + d] * f;
+      }
+    }
+  }
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
   T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
@@ -240,6 +284,28 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   for (int r = 0; r < VR; ++r) {
     const int d = lane + 32 * r;
     if (d < vdim) orow[d] = cvt<T>(acc[r] / l * gate);
+  }
+}
+
+__global__ void __launch_bounds__(256) stack_bias_add_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ b,
+                                                             int n, int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
+    y[e] = __float2bfloat16_rn(__bfloat162float(y[e]) + b[e % n]);
+}
+__global__ void __launch_bounds__(256) stack_axpy_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ t,
+                                                         float mult, int add, int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
+    x[e] = (add ? x[e] : 0.f) + mult * __bfloat162float(t[e]);
+}
+__global__ void __launch_bounds__(256) stack_cat_cast_kernel(__nv_bfloat16* __restrict__ cat, const float* __restrict__ a,
+                                                             const float* __restrict__ b, float* __restrict__ zero,
+                                                             int width, int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / width;
+    const int j = (int)(e % width);
+    cat[r * 2 * width + j] = __float2bfloat16_rn(a[e]);
+    cat[r * 2 * width + width + j] = __float2bfloat16_rn(b[e]);
+    if (zero != nullptr) zero[e] = 0.f;
   }
 }
 
@@ -313,6 +379,28 @@ int launch_stack_embed(float* x, float* x0, const void* embed, const int32_t* to
   return B200_OK;
 }
 
+int launch_stack_bias_add(__nv_bfloat16* y, const float* b, int64_t rows, int n, cudaStream_t st) {
+  B200_CHECK_ARG(y && b && rows > 0 && n > 0, "stack bias_add: bad arguments");
+  const int64_t total = rows * n;
+  B200_CUDA(launch_pdl(stack_bias_add_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, b, n, total));
+  return B200_OK;
+}
+
+int launch_stack_axpy(float* x, const __nv_bfloat16* t, float mult, bool add, int64_t total, cudaStream_t st) {
+  B200_CHECK_ARG(x && t && total > 0, "stack axpy: bad arguments");
+  B200_CUDA(launch_pdl(stack_axpy_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, x, t, mult, add ? 1 : 0, total));
+  return B200_OK;
+}
+
+int launch_stack_cat_cast(__nv_bfloat16* cat, const float* a, const float* b, float* zero, int64_t rows, int width,
+                          cudaStream_t st) {
+  B200_CHECK_ARG(cat && a && b && rows > 0 && width > 0, "stack cat_cast: bad arguments");
+  const int64_t total = rows * width;
+  B200_CUDA(launch_pdl(stack_cat_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, cat, a, b, zero, width,
+                       total));
+  return B200_OK;
+}
+
 static int check_attn(const StackAttn& p) {
   const b200_attn_desc& a = p.a;
   B200_CHECK_ARG(a.heads > 0 && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.dim > 0 && a.vdim > 0,
@@ -333,16 +421,17 @@ int launch_stack_kv_store(const StackAttn& p, int dtype, cudaStream_t st) {
   return B200_OK;
 }
 
-template <typename T>
+template <typename T, int NW, bool VEC>
 static cudaError_t launch_attn_t(const StackAttn& p, cudaStream_t st) {
   const int64_t pairs = (int64_t)p.n_tok * p.a.heads;
-  const dim3 grid((unsigned)((pairs + 3) / 4));
-  const size_t smem = (size_t)4 * p.a.dim * sizeof(float);
+  const int ppb = 4 / NW;
+  const dim3 grid((unsigned)((pairs + ppb - 1) / ppb));
+  const size_t smem = ((size_t)4 * p.a.dim + (NW > 1 ? (size_t)NW * (2 + p.a.vdim) : 0)) * sizeof(float);
   const int vr = (p.a.vdim + 31) / 32;
-  if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1>, grid, dim3(128), smem, st, false, p);
-  if (vr <= 2) return launch_pdl(stack_attn_kernel<T, 2>, grid, dim3(128), smem, st, false, p);
-  if (vr <= 4) return launch_pdl(stack_attn_kernel<T, 4>, grid, dim3(128), smem, st, false, p);
-  return launch_pdl(stack_attn_kernel<T, 8>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1, NW, VEC>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 2) return launch_pdl(stack_attn_kernel<T, 2, NW, VEC>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 4) return launch_pdl(stack_attn_kernel<T, 4, NW, VEC>, grid, dim3(128), smem, st, false, p);
+  return launch_pdl(stack_attn_kernel<T, 8, NW, VEC>, grid, dim3(128), smem, st, false, p);
 }
 
 int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
@@ -350,8 +439,20 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
   int rc = check_attn(p);
   if (rc != B200_OK) return rc;
   B200_CHECK_ARG(p.out != nullptr, "stack attention: null output");
-  if (dtype == B200_F32) B200_CUDA(launch_attn_t<float>(p, st));
-  else B200_CUDA(launch_attn_t<__nv_bfloat16>(p, st));
+  // few (token, head) pairs: four warps share one pair's keys
+  const bool wide = (int64_t)p.n_tok * p.a.heads < 4 * 148 * 4;
+  const bool vec = dtype == B200_BF16 && p.a.dim % 8 == 0 && p.k_slot_stride % 8 == 0 &&
+                   (reinterpret_cast<uintptr_t>(p.kcache) & 15) == 0;
+  if (dtype == B200_F32) {
+    if (wide) B200_CUDA((launch_attn_t<float, 4, false>(p, st)));
+    else B200_CUDA((launch_attn_t<float, 1, false>(p, st)));
+  } else if (vec) {
+    if (wide) B200_CUDA((launch_attn_t<__nv_bfloat16, 4, true>(p, st)));
+    else B200_CUDA((launch_attn_t<__nv_bfloat16, 1, true>(p, st)));
+  } else {
+    if (wide) B200_CUDA((launch_attn_t<__nv_bfloat16, 4, false>(p, st)));
+    else B200_CUDA((launch_attn_t<__nv_bfloat16, 1, false>(p, st)));
+  }
   return B200_OK;
 }
 
