@@ -674,7 +674,15 @@ def main():
                     help="skip the other BASELINE configs (Llama-3.2-3B, Qwen3-1.7B prefill, Mistral-7B TP) in the same job")
     ap.add_argument("--mode", default="tp", choices=["tp", "replicas"],
                     help="N > 1: tensor parallel over one sequence (default, strong scaling) or independent replicas")
+    ap.add_argument("--stack-compare", nargs="?", const="all", default=None, metavar="SIZES",
+                    help="instead of the headline run: prefill / decode throughput of the Kozusun layer-stack design beside "
+                         "the Llama-family model of equal size (comma-separated sizes of tinygpt_b200/stack_bench.py, or all)")
     args = ap.parse_args()
+    if args.stack_compare is not None:
+        from tinygpt_b200 import build, stack_bench
+        build.build()
+        stack_bench.main(args.stack_compare, steps=max(1, min(args.steps, 10)), warmup=max(3, args.warmup))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -296,6 +296,33 @@ def test_other_sizes_and_layer_orders(dtype, name):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd", [64, 128])
+def test_long_prompts_big_heads_and_split_keys(dtype, hd):
+    """Head sizes the tensor-core prompt attention takes (bf16), windows whose edges cross its 64-key tiles, kept tokens
+    in a tile of their own, and decode steps whose key lists are long enough to be split over CTAs."""
+    cfg = so.make_config(width=64, vocab=80, side_dim=8, loop=(0, 1, 2),
+                         layers=[dict(heads=2, kv_heads=1, dim=hd, vdim=hd, size=70, keep_first=5, ff=32),
+                                 dict(heads=2, kv_heads=2, dim=hd, vdim=hd, size=300, keep_first=0, ff=32)])
+    w = so.make_weights(cfg, seed=12)
+    n0, n1 = 171, 8
+    toks = tokens(n0 + n1, cfg["vocab"], 13)
+    short = tokens(20, cfg["vocab"], 14)
+    want, want_short = so.forward(cfg, w, toks), so.forward(cfg, w, short)
+    eng = make_engine(cfg, w, dtype, max_ctx=420)
+    # a long and a short prompt together, the long one cut so that its second part starts inside a tile
+    got = eng.step([(0, toks[:100], list(range(100))), (1, short[:17], list(range(17)))])
+    assert rel_err(got[:100], want[:100]) < TOL[dtype]
+    assert rel_err(got[100:], want_short[:17]) < TOL[dtype]
+    got = eng.step([(0, toks[100:n0], list(range(n0 - 100))), (1, short[17:], [0, 1, 2])])
+    assert rel_err(got[:n0 - 100], want[100:n0]) < TOL[dtype]
+    assert rel_err(got[n0 - 100:], want_short[17:]) < TOL[dtype]
+    eng.release(1)
+    rows = [eng.step([(0, [toks[t]], [0])]) for t in range(n0, n0 + n1)]
+    assert rel_err(torch.cat(rows), want[n0:]) < TOL[dtype]
+    eng.close()
+
+
 def test_residual_stream_mechanisms_show_in_the_logits():
     """Each constant matters: dropping the kept tokens, shifting the window by one, dropping the side input or the loop's
     re-read of the embedding moves the oracle's logits by far more than the engine's distance to the true design."""

@@ -16,6 +16,7 @@
 // then rmsnorm of the wanted rows only and the head product (fp32 logits + the bf16 copy argmax / sampler read).
 #include <algorithm>
 #include <cstring>
+#include <map>
 #include <new>
 #include <vector>
 
@@ -63,13 +64,25 @@ struct StackEngine {
   bool fast = false;
   int num_sms = 148;
   struct Plans {
-    GemvPlan in{}, out{};
-    bool ok_in = false, ok_out = false;
+    GemvPlan in{}, out{}, side_gate{}, side_proj{};
+    bool ok_in = false, ok_out = false, ok_side = false;
   };
+  // the step's sequences as row ranges of the row list (host mirror; empty for decode steps): the tensor-core prompt
+  // attention runs per sequence
+  struct Seg {
+    int row0, count, slot, pos0;
+  };
+  std::vector<Seg> segs;
+  float* attn_ws = nullptr;       // split-key partials of decode steps
+  int max_heads = 1, max_vdim = 1;
   std::vector<Plans> plans;
   GemvPlan p_mix{}, p_head{};
   bool ok_mix = false, ok_head = false;
   __nv_bfloat16* cat = nullptr;   // bf16 [x | x0] rows for the mix-in product
+  // greedy decode steps as CUDA graphs, one per number of rows (row → slot goes through row_slot on the device, so a
+  // graph outlives changes of the active set); dropped when the workspace moves
+  std::map<int, cudaGraphExec_t> g_dec;
+  std::map<int, int> g_launches_of;
 };
 constexpr int kGemmRows = 32;
 
@@ -124,6 +137,8 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
     B200_CUDA(cudaDeviceSynchronize());
     cudaFree(s->ws);
     s->ws = nullptr;
+    for (auto& kv : s->g_dec) cudaGraphExecDestroy(kv.second);
+    s->g_dec.clear();
   }
   const b200_stack_desc& d = s->d;
   size_t off = 0;
@@ -140,6 +155,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_lb = take((size_t)rows * d.vocab * 2);
   const size_t o_meta = take((3 * T + rows + 2 * (size_t)d.max_slots) * 4);
   const size_t o_cat = take(d.mix_in != nullptr && s->dtype == B200_BF16 ? T * 2 * W * 2 : 0);
+  const size_t o_aws = take((size_t)kStackSplitRows * s->max_heads * kStackMaxSplits * (2 + s->max_vdim) * 4);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->ws_tok = tok;
@@ -161,6 +177,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->m_want = s->m_pos + T;
   s->m_upd = s->m_want + rows;
   s->cat = (__nv_bfloat16*)(s->ws + o_cat);
+  s->attn_ws = (float*)(s->ws + o_aws);
   return B200_OK;
 }
 
@@ -259,6 +276,98 @@ static int stack_product_head(StackEngine* s, int n_rows, cudaStream_t st) {
   return launch_stack_gemm(g, s->dtype, st);
 }
 
+// Attention of a run over the step's rows.  bf16 engines with equal key / value head sizes of 64 or 128 send every
+// sequence that brings kTcRows rows or more to the tensor-core kernel (prefill_attn.cu), one launch per sequence; what is
+// left (short parts, decode tokens, other head sizes, fp32) goes to the general kernel, with the keys split over CTAs when
+// the step is a handful of rows over a long key list.
+constexpr int kTcRows = 16;
+static int stack_attention(StackEngine* s, const StackAttn& a, const b200_stack_layer& L, cudaStream_t st) {
+  const b200_attn_desc& d = L.attn;
+  const int dt = s->dtype;
+  int rc;
+  auto general = [&](int row0, int count) {
+    StackAttn q = a;
+    q.proj = (const uint8_t*)a.proj + (size_t)row0 * a.ld_proj * s->esz;
+    q.out = (uint8_t*)a.out + (size_t)row0 * a.ld_out * s->esz;
+    q.slot = a.slot + row0;
+    q.pos = a.pos + row0;
+    q.n_tok = count;
+    const int kmax = d.window > 0 ? std::min(d.window + d.keep_first, s->d.max_ctx) : s->d.max_ctx;
+    const int nsplit = std::min(kStackMaxSplits, (kmax + kStackSplitKeys - 1) / kStackSplitKeys);
+    if (count <= kStackSplitRows && nsplit > 1) {
+      q.split_ws = s->attn_ws;
+      q.nsplit = nsplit;
+      q.keys_per_split = ((kmax + nsplit - 1) / nsplit + 31) / 32 * 32;
+    }
+    return launch_stack_attention(q, dt, st);
+  };
+  const bool tc = s->fast && d.dim == d.vdim && (d.dim == 64 || d.dim == 128);
+  bool any = false;
+  for (const StackEngine::Seg& g : s->segs) any = any || g.count >= kTcRows;
+  if (!tc || !any) return general(0, a.n_tok);
+  for (const StackEngine::Seg& g : s->segs) {
+    if (g.count < kTcRows) {
+      if ((rc = general(g.row0, g.count)) != B200_OK) return rc;
+      continue;
+    }
+    const __nv_bfloat16* prow = (const __nv_bfloat16*)a.proj + (size_t)g.row0 * a.ld_proj;
+    if ((rc = launch_attn_prefill_window((__nv_bfloat16*)a.out + (size_t)g.row0 * a.ld_out, a.ld_out, prow + a.off_q,
+                                         d.out_gate ? prow + a.off_g : nullptr, a.ld_proj,
+                                         (const __nv_bfloat16*)a.kcache + (size_t)g.slot * a.k_slot_stride,
+                                         (const __nv_bfloat16*)a.vcache + (size_t)g.slot * a.v_slot_stride, g.count, d.heads,
+                                         d.kv_heads, d.dim, g.pos0, d.scale, d.window, d.keep_first, st)) != B200_OK)
+      return rc;
+  }
+  return B200_OK;
+}
+
+// x += m · rmsnorm(side_proj·(gelu(side_gate·x) ∘ table[token]))·w_side
+static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_t st) {
+  const b200_stack_desc& d = s->d;
+  const b200_stack_layer& L = s->layers[li];
+  const int W = d.width, sd = d.side_dim;
+  int rc;
+  const bool gemv = s->fast && n_tok <= kMaxBatch && s->plans[li].ok_side;
+  const bool gemm = s->fast && n_tok >= kGemmRows && gemm_shape_ok(sd, W) && gemm_shape_ok(W, sd);
+  if (gemv || gemm) {
+    // bf16 operand of the stream in h, the gate product in proj (both are free here), the gated table row in sg
+    __nv_bfloat16 *xb = (__nv_bfloat16*)s->h, *raw = (__nv_bfloat16*)s->proj, *sg = (__nv_bfloat16*)s->sg;
+    if ((rc = launch_stack_cast(xb, cur, (int64_t)n_tok * W, st)) != B200_OK) return rc;
+    if (gemv) {
+      GemvPlan pl = s->plans[li].side_gate;
+      pl.p.x = xb;
+      pl.p.y = raw;
+      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, false)) != B200_OK) return rc;
+    } else if ((rc = launch_gemm_bf16(raw, xb, L.side_gate, n_tok, sd, W, st)) != B200_OK) {
+      return rc;
+    }
+    if ((rc = launch_stack_act_table(sg, raw, d.side_table, s->m_tok, d.side_stride, L.side_col, n_tok, sd, st)) != B200_OK)
+      return rc;
+    if (gemv) {
+      GemvPlan pl = s->plans[li].side_proj;
+      pl.p.x = sg;
+      pl.p.y = xb;          // the rounded copy is not used
+      pl.p.yf = s->y;
+      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, false)) != B200_OK) return rc;
+      return launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st);
+    }
+    if ((rc = launch_gemm_bf16(xb, sg, L.side_proj, n_tok, W, sd, st)) != B200_OK) return rc;
+    return launch_stack_rms_add_bf16(cur, xb, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st);
+  }
+  StackGemm g;
+  g.a = cur; g.lda = W; g.k1 = W; g.a_f32 = true;
+  g.w = L.side_gate; g.M = n_tok; g.N = sd; g.K = W;
+  g.epi = SEPI_ACT_TABLE; g.c = s->sg; g.ldc = sd;
+  g.table = d.side_table; g.tok = s->m_tok; g.table_ld = d.side_stride; g.table_col = L.side_col;
+  if ((rc = launch_stack_gemm(g, s->dtype, st)) != B200_OK) return rc;
+  StackGemm p;
+  p.a = s->sg; p.lda = sd; p.k1 = sd;
+  p.w = L.side_proj; p.M = n_tok; p.N = W; p.K = sd;
+  p.epi = SEPI_STORE_F32; p.c = s->y; p.ldc = W;
+  if ((rc = launch_stack_gemm(p, s->dtype, st)) != B200_OK) return rc;
+  return launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st);
+}
+
 // One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
 static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
   StackEngine* s = e->stack;
@@ -290,7 +399,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
     if (hv != L.off_act || L.off_act + L.ff != L.k_out)   // padding columns meet zero weights: keep them finite
       B200_CUDA(cudaMemsetAsync(s->mid, 0, (size_t)n_tok * L.k_out * s->esz, st));
     if ((rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
-    if ((rc = launch_stack_attention(a, dt, st)) != B200_OK) return rc;
+    if ((rc = stack_attention(s, a, L, st)) != B200_OK) return rc;
     if (L.ff > 0) {
       const uint8_t* p = (const uint8_t*)s->proj;
       if ((rc = launch_stack_act_mul((uint8_t*)s->mid + (size_t)L.off_act * s->esz, L.k_out, p + (size_t)L.off_gate * s->esz,
@@ -298,21 +407,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
         return rc;
     }
     if ((rc = stack_product_out(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
-    if (L.side_gate != nullptr) {
-      StackGemm g;
-      g.a = cur; g.lda = W; g.k1 = W; g.a_f32 = true;
-      g.w = L.side_gate; g.M = n_tok; g.N = d.side_dim; g.K = W;
-      g.epi = SEPI_ACT_TABLE; g.c = s->sg; g.ldc = d.side_dim;
-      g.table = d.side_table; g.tok = s->m_tok; g.table_ld = d.side_stride; g.table_col = L.side_col;
-      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
-      StackGemm p;
-      p.a = s->sg; p.lda = d.side_dim; p.k1 = d.side_dim;
-      p.w = L.side_proj; p.M = n_tok; p.N = W; p.K = d.side_dim;
-      p.epi = SEPI_STORE_F32; p.c = s->y; p.ldc = W;
-      if ((rc = launch_stack_gemm(p, dt, st)) != B200_OK) return rc;
-      if ((rc = launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st)) != B200_OK)
-        return rc;
-    }
+    if (L.side_gate != nullptr && (rc = stack_side(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
   }
   if (n_rows > 0) {
     if ((rc = launch_stack_rmsnorm(s->hn, cur, d.final_norm, s->m_want, n_rows, W, d.norm_eps, d.norm_offset, dt, st)) !=
@@ -350,8 +445,10 @@ static int stack_publish(b200_engine* e, int row0, const std::vector<int>& slots
     pub.row_slot = s->row_slot;
     if ((rc = launch_argmax(s->amax_out, lg, n, s->d.vocab, s->argmax_ws, st, false, &pub)) != B200_OK) return rc;
   }
-  for (int sl : slots) s->h_gen[sl] += 1;
   return B200_OK;
+}
+static void stack_count_generated(StackEngine* s, const std::vector<int>& slots, int64_t n) {
+  for (int sl : slots) s->h_gen[sl] += n;
 }
 
 static int stack_set_active(StackEngine* s, const std::vector<int>& slots, cudaStream_t st) {
@@ -365,6 +462,7 @@ static int stack_set_active(StackEngine* s, const std::vector<int>& slots, cudaS
 void stack_destroy(b200_engine* e) {
   StackEngine* s = e->stack;
   if (!s) return;
+  for (auto& kv : s->g_dec) cudaGraphExecDestroy(kv.second);
   if (s->cache) cudaFree(s->cache);
   if (s->state) cudaFree(s->state);
   if (s->ws) cudaFree(s->ws);
@@ -453,6 +551,8 @@ int stack_forward(b200_engine* e, const int64_t* ids, int64_t B, int64_t S, void
                            (int)B, cs));
       n_rows += (int)B;
     }
+    s->segs.clear();
+    for (int b = 0; b < B; ++b) s->segs.push_back({b * cs, cs, b, (int)s->h_pos[b] + (int)s0});
     if ((rc = stack_pass(e, n_tok, n_rows, st)) != B200_OK) return rc;
     if (all)   // rows are [b][t of this chunk] → logits_out [B][S][V]
       B200_CUDA(cudaMemcpy2DAsync((uint8_t*)logits_out + (size_t)s0 * vb, (size_t)S * vb, s->logits_bf, (size_t)cs * vb,
@@ -471,8 +571,52 @@ int stack_forward(b200_engine* e, const int64_t* ids, int64_t B, int64_t S, void
   e->h_pos = s->h_pos[0];
   e->batch = (int)B;
   // the greedy token of every sequence's last position becomes its slot's current token
+  stack_count_generated(s, slots, 1);
   return stack_publish(e, head_row0, slots, st);
 }
+
+// one greedy decode step of the active batch: row list from the slots' device state, the pass, the publication
+static int stack_decode_step(b200_engine* e, int B, cudaStream_t st) {
+  StackEngine* s = e->stack;
+  int rc;
+  B200_CUDA(launch_pdl(stack_meta_decode_kernel, dim3((B + 63) / 64), dim3(64), 0, st, false, (const int*)s->row_slot, B,
+                       s->pos_dev, (const int64_t*)s->cur_tok, s->m_tok, s->m_slot, s->m_pos, s->m_want));
+  s->segs.clear();
+  if ((rc = stack_pass(e, B, B, st)) != B200_OK) return rc;
+  return stack_publish(e, 0, s->active, st);
+}
+
+static int stack_capture_decode(b200_engine* e, int B) {
+  StackEngine* s = e->stack;
+  cudaStream_t st;
+  B200_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+  cudaGraph_t g = nullptr;
+  cudaError_t err = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+  if (err != cudaSuccess) {
+    cudaStreamDestroy(st);
+    set_error("cudaStreamBeginCapture failed: %s", cudaGetErrorString(err));
+    return B200_ERR_CUDA;
+  }
+  const int64_t before = g_launches.load();
+  int rc = stack_decode_step(e, B, st);
+  const int64_t n = g_launches.load() - before;
+  g_launches.fetch_sub(n);   // capture does not execute anything
+  err = cudaStreamEndCapture(st, &g);
+  cudaGraphExec_t ex = nullptr;
+  if (rc == B200_OK && err == cudaSuccess) err = cudaGraphInstantiate(&ex, g, 0);
+  if (g) cudaGraphDestroy(g);
+  cudaStreamDestroy(st);
+  if (rc != B200_OK) return rc;
+  if (err != cudaSuccess) {
+    set_error("stack decode graph: %s", cudaGetErrorString(err));
+    return B200_ERR_CUDA;
+  }
+  s->g_dec[B] = ex;
+  s->g_launches_of[B] = (int)n;
+  e->launches_per_token = (int)n;
+  return B200_OK;
+}
+
 
 int stack_decode(b200_engine* e, int64_t n_steps, int64_t* tokens_out, cudaStream_t st) {
   StackEngine* s = e->stack;
@@ -489,12 +633,17 @@ int stack_decode(b200_engine* e, int64_t n_steps, int64_t* tokens_out, cudaStrea
   if (rc != B200_OK) return rc;
   std::vector<int64_t> first(B);
   for (int r = 0; r < B; ++r) first[r] = s->h_gen[s->active[r]];
+  const bool graph = e->use_graph && !e->sampler_on;   // the sampler's publication is bound to slots on the host
+  if (graph && n_steps > 0 && s->g_dec.find(B) == s->g_dec.end() && (rc = stack_capture_decode(e, B)) != B200_OK) return rc;
   for (int64_t i = 0; i < n_steps; ++i) {
-    B200_CUDA(launch_pdl(stack_meta_decode_kernel, dim3((B + 63) / 64), dim3(64), 0, st, false, (const int*)s->row_slot, B,
-                         s->pos_dev, (const int64_t*)s->cur_tok, s->m_tok, s->m_slot, s->m_pos, s->m_want));
-    if ((rc = stack_pass(e, B, B, st)) != B200_OK) return rc;
-    if ((rc = stack_publish(e, 0, s->active, st)) != B200_OK) return rc;
+    if (graph) {
+      B200_CUDA(cudaGraphLaunch(s->g_dec[B], st));
+      g_launches.fetch_add(s->g_launches_of[B]);
+    } else if ((rc = stack_decode_step(e, B, st)) != B200_OK) {
+      return rc;
+    }
   }
+  stack_count_generated(s, s->active, n_steps);
   for (int sl : s->active) s->h_pos[sl] += n_steps;
   e->h_pos = s->h_pos[s->active[0]];
   if (tokens_out != nullptr && n_steps > 0) {   // [n_steps][B] from the slots' own logs
@@ -592,7 +741,9 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     B200_CHECK_ARG(L.side_gate == nullptr || (L.side_proj && L.side_norm && d.side_table && d.side_dim > 0 &&
                                               L.side_col + d.side_dim <= d.side_stride),
                    "engine_create_stack: layer %d: incomplete side input", l);
-    s->n_in_max = std::max(s->n_in_max, L.n_in);
+    s->max_heads = std::max(s->max_heads, a.heads);
+    s->max_vdim = std::max(s->max_vdim, a.vdim);
+    s->n_in_max = std::max(s->n_in_max, std::max(L.n_in, d.side_dim));
     s->k_out_max = std::max(s->k_out_max, L.k_out);
   }
   s->run_k_off.resize(d.n_runs);
@@ -626,6 +777,9 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       const b200_stack_layer& L = s->layers[l];
       s->plans[l].ok_in = plan(&s->plans[l].in, L.w_in, L.n_in, d.width, EPI_BIAS_F32);
       s->plans[l].ok_out = plan(&s->plans[l].out, L.w_out, d.width, L.k_out, EPI_RESID_F32);
+      s->plans[l].ok_side = L.side_gate != nullptr &&
+                            plan(&s->plans[l].side_gate, L.side_gate, d.side_dim, d.width, EPI_BIAS_F32) &&
+                            plan(&s->plans[l].side_proj, L.side_proj, d.width, d.side_dim, EPI_BIAS_F32);
     }
     if (d.mix_in) s->ok_mix = plan(&s->p_mix, d.mix_in, d.width, 2 * (int64_t)d.width, EPI_RESID_F32);
     s->ok_head = plan(&s->p_head, d.head, d.vocab, d.width, EPI_BIAS_F32);
@@ -661,7 +815,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   e->d.max_ctx = d.max_ctx;
   e->d.layers = d.n_layers;
   e->V_l = d.vocab;
-  e->use_graph = false;
+  e->use_graph = !env_flag("B200_NO_GRAPH", false);
   e->use_pdl = false;
   guard.e = nullptr;
   *out = e;
@@ -750,6 +904,12 @@ int b200_engine_step(b200_engine* e, int64_t n_seq, const int32_t* slots, const 
     B200_CUDA(cudaMemcpyAsync(s->m_slot, slot.data() + c0, (size_t)n_tok * 4, cudaMemcpyHostToDevice, st));
     B200_CUDA(cudaMemcpyAsync(s->m_pos, pos.data() + c0, (size_t)n_tok * 4, cudaMemcpyHostToDevice, st));
     if (n_rows > 0) B200_CUDA(cudaMemcpyAsync(s->m_want, rows.data(), (size_t)n_rows * 4, cudaMemcpyHostToDevice, st));
+    s->segs.clear();
+    for (int t = 0; t < n_tok; ++t) {
+      const int64_t gi = c0 + t;
+      if (t == 0 || slot[gi] != slot[gi - 1]) s->segs.push_back({t, 1, slot[gi], pos[gi]});
+      else s->segs.back().count += 1;
+    }
     if ((rc = stack_pass(e, n_tok, n_rows, st)) != B200_OK) return rc;
     for (int r = 0; r < n_user;) {   // runs of consecutive destination rows leave in one copy
       int r1 = r + 1;
@@ -758,7 +918,10 @@ int b200_engine_step(b200_engine* e, int64_t n_seq, const int32_t* slots, const 
                                 (size_t)(r1 - r) * vb4, cudaMemcpyDeviceToDevice, st));
       r = r1;
     }
-    if (greedy && tail && (rc = stack_publish(e, n_user, act_slots, st)) != B200_OK) return rc;
+    if (greedy && tail) {
+      stack_count_generated(s, act_slots, 1);
+      if ((rc = stack_publish(e, n_user, act_slots, st)) != B200_OK) return rc;
+    }
   }
   std::vector<int32_t> upd;
   for (int64_t i = 0; i < n_seq; ++i) {

@@ -73,6 +73,11 @@ struct PrefillAttnParams {
   const __nv_bfloat16* v;
   int64_t o_rs, o_bs, q_rs, q_bs, kv_rs, kv_bs;
   int S, Hq, Hkv, p0;
+  float scale_log2;             // score scale × log2(e)  (Llama family: log2(e)/√hd)
+  // sliding window with kept first keys (layer-stack models): key j is visible from the query at position i when
+  // j <= i and (window == 0 or i − j < window or j < keep_first)
+  int window, keep_first;
+  const __nv_bfloat16* gate;    // per-head gate logits, head h of row r at gate + b*q_bs + r*q_rs + h; null = none
 };
 
 // byte offset of 16-byte chunk c of row r inside a [rows][HD] bf16 tile (chunks XOR-swizzled within groups of 8)
@@ -86,7 +91,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
   constexpr int CH = HD / 8;    // 16-byte chunks per row
   constexpr int KS = HD / 16;   // k-steps of Q·Kᵀ
   constexpr int ND = HD / 8;    // 8-wide output column blocks of O
-  constexpr float kScale = PfScale<HD>::value;
+  const float kScale = p.scale_log2;
 
   extern __shared__ __align__(128) uint8_t pf_smem[];
   uint8_t* const Qs = pf_smem;                       // [kBM][HD]
@@ -102,6 +107,13 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
   const int rows_valid = min(kBM, p.S - q0);
   const int nkeys = p.p0 + q0 + rows_valid;              // keys the last valid row of this block sees
   const int T = (nkeys + kBN - 1) / kBN;
+  // tiles to visit: with a window only those from the first row's window edge up to the diagonal, then the tiles of
+  // the kept first keys that lie below them
+  const int t_lo = p.window > 0 ? max(0, p.p0 + q0 - p.window + 1) / kBN : 0;
+  const int n_win = T - t_lo;
+  const int n_keep = p.window > 0 ? min(t_lo, (p.keep_first + kBN - 1) / kBN) : 0;
+  const int n_tiles = n_win + n_keep;
+  auto tile_of = [&](int it) { return it < n_win ? T - 1 - it : n_keep - 1 - (it - n_win); };
 
   const __nv_bfloat16* qg = p.q + (size_t)b * p.q_bs + (size_t)h * HD;
   const __nv_bfloat16* kg = p.k + (size_t)b * p.kv_bs + (size_t)kvh * HD;
@@ -133,7 +145,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
     }
     pf_commit();
   };
-  load_kv(T - 1, 0);
+  load_kv(tile_of(0), 0);
 
   uint32_t qf[KS][4];
   float o_acc[ND][4];
@@ -150,10 +162,10 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
 
   const uint32_t qs_u = smem_u32(Qs), ks_u = smem_u32(Ks), vs_u = smem_u32(Vs);
 
-  for (int it = 0; it < T; ++it) {
-    const int t = T - 1 - it, buf = it & 1;
-    if (it + 1 < T) {
-      load_kv(t - 1, buf ^ 1);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int t = tile_of(it), buf = it & 1;
+    if (it + 1 < n_tiles) {
+      load_kv(tile_of(it + 1), buf ^ 1);
       pf_wait<1>();
     } else {
       pf_wait<0>();
@@ -185,7 +197,17 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
 
     // ---- causal mask (only tiles that reach past the block's first row can contain masked keys)
     const int kbase = t * kBN;
-    if (kbase + kBN - 1 > p.p0 + q0) {
+    if (p.window > 0) {
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = kbase + n * 8 + 2 * tq + (e & 1);
+          const int i = rpos[e >> 1];
+          if (j > i || (i - j >= p.window && j >= p.keep_first)) s[n][e] = -INFINITY;
+        }
+      }
+    } else if (kbase + kBN - 1 > p.p0 + q0) {
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
         const int j = kbase + n * 8 + 2 * tq;
@@ -246,9 +268,11 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
     float l = l_run[rr];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float inv = l > 0.f ? 1.f / l : 0.f;
     const int r = warp * 16 + g + 8 * rr;
     if (r < rows_valid) {
+      if (p.gate != nullptr)
+        inv *= 1.f / (1.f + expf(-bf16_to_f(p.gate[(size_t)b * p.q_bs + (size_t)(q0 + r) * p.q_rs + h])));
       __nv_bfloat16* dst = p.o + (size_t)b * p.o_bs + (size_t)(q0 + r) * p.o_rs + (size_t)h * HD + 2 * tq;
 #pragma unroll
       for (int n = 0; n < ND; ++n)
@@ -296,6 +320,38 @@ int launch_attn_prefill_mma(void* o, const void* qkv, const void* kcache, const 
   p.Hq = Hq;
   p.Hkv = Hkv;
   p.p0 = p0;
+  p.scale_log2 = hd == 64 ? PfScale<64>::value : PfScale<128>::value;
+  return hd == 64 ? launch_pf<64>(p, 1, st) : launch_pf<128>(p, 1, st);
+}
+
+// Layer-stack models: one sequence's rows of a step (positions p0 … p0+S-1) against that sequence's cache, with an
+// explicit score scale, a sliding window with kept first keys and a per-head sigmoid gate on the output.  q (and the
+// gate logits) are column ranges of the merged projection rows (stride q_rs), o a column range of rows of stride o_rs.
+int launch_attn_prefill_window(void* o, int64_t o_rs, const void* q, const void* gate_or_null, int64_t q_rs,
+                               const void* kcache, const void* vcache, int S, int Hq, int Hkv, int hd, int p0, float scale,
+                               int window, int keep_first, cudaStream_t st) {
+  B200_CHECK_ARG(hd == 64 || hd == 128, "prefill attention: head size %d not built", hd);
+  B200_CHECK_ARG(S > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq < 65536 && p0 >= 0 && window >= 0 && keep_first >= 0,
+                 "prefill attention: bad shape");
+  B200_CHECK_ARG(((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kcache) | reinterpret_cast<uintptr_t>(vcache)) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(o) & 3) == 0 && q_rs % 8 == 0 && o_rs % 2 == 0,
+                 "prefill attention: operands must be 16-byte aligned");
+  PrefillAttnParams p{};
+  p.o = (__nv_bfloat16*)o;
+  p.q = (const __nv_bfloat16*)q;
+  p.k = (const __nv_bfloat16*)kcache;
+  p.v = (const __nv_bfloat16*)vcache;
+  p.gate = (const __nv_bfloat16*)gate_or_null;
+  p.o_rs = o_rs;
+  p.q_rs = q_rs;
+  p.kv_rs = (int64_t)Hkv * hd;
+  p.S = S;
+  p.Hq = Hq;
+  p.Hkv = Hkv;
+  p.p0 = p0;
+  p.scale_log2 = scale * kLog2eP;
+  p.window = window;
+  p.keep_first = keep_first;
   return hd == 64 ? launch_pf<64>(p, 1, st) : launch_pf<128>(p, 1, st);
 }
 
@@ -318,6 +374,7 @@ int launch_attn_causal_mma(void* o, const void* q, const void* k, const void* v,
   p.Hq = (int)Hq;
   p.Hkv = (int)Hkv;
   p.p0 = 0;
+  p.scale_log2 = hd == 64 ? PfScale<64>::value : PfScale<128>::value;
   return hd == 64 ? launch_pf<64>(p, (int)B, st) : launch_pf<128>(p, (int)B, st);
 }
 

@@ -57,6 +57,13 @@ int launch_stack_axpy(float* x, const __nv_bfloat16* t, float mult, bool add, in
 int launch_stack_cat_cast(__nv_bfloat16* cat, const float* a, const float* b, float* zero_or_null, int64_t rows, int width,
                           cudaStream_t st);
 
+int launch_stack_rms_add_bf16(float* x, const __nv_bfloat16* y, const float* w, int64_t rows, int dim, float eps, float mult,
+                              cudaStream_t st);
+int launch_stack_cast(__nv_bfloat16* y, const float* x, int64_t total, cudaStream_t st);
+// y[r, j] = bf16(gelu_tanh(g[r, j]) · table[tok[r], col + j])
+int launch_stack_act_table(__nv_bfloat16* y, const __nv_bfloat16* g, const void* table, const int32_t* tok, int64_t table_ld,
+                           int col, int64_t rows, int n, cudaStream_t st);
+
 struct StackAttn {
   b200_attn_desc a{};
   const void* proj = nullptr;   // [n_tok, ld_proj] T: q at off_q (heads·dim), k at off_k, v at off_v, gate logits at off_g
@@ -70,7 +77,14 @@ struct StackAttn {
   int n_tok = 0;
   void* out = nullptr;          // [n_tok, ld_out] T, head h at columns h·vdim
   int64_t ld_out = 0;
+  // split keys (decode steps over long key lists): nsplit CTAs per (token, head), each over keys_per_split entries of
+  // the visible list, partial softmaxes [n_tok·heads][nsplit][2 + vdim] in split_ws, merged by a second launch
+  float* split_ws = nullptr;
+  int nsplit = 1, keys_per_split = 0;
 };
+constexpr int kStackSplitRows = 16;    // most rows a split-key attention launch serves
+constexpr int kStackSplitKeys = 128;   // keys per split
+constexpr int kStackMaxSplits = 64;
 int launch_stack_kv_store(const StackAttn& p, int dtype, cudaStream_t st);
 int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st);
 

@@ -125,15 +125,34 @@ __global__ void __launch_bounds__(256) stack_rmsnorm_kernel(T* __restrict__ y, c
   for (int i = threadIdx.x; i < dim; i += blockDim.x) yr[i] = cvt<T>(xr[i] * inv * (offset + w[i]));
 }
 
-__global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ x, const float* __restrict__ y,
+template <typename YT>
+__global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ x, const YT* __restrict__ y,
                                                             const float* __restrict__ w, int dim, float eps, float mult) {
   __shared__ float red[8];
-  const float* yr = y + (int64_t)blockIdx.x * dim;
+  const YT* yr = y + (int64_t)blockIdx.x * dim;
   float* xr = x + (int64_t)blockIdx.x * dim;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += yr[i] * yr[i];
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += ldf<YT>(yr + i) * ldf<YT>(yr + i);
   const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += mult * (yr[i] * inv * w[i]);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += mult * (ldf<YT>(yr + i) * inv * w[i]);
+}
+
+__global__ void __launch_bounds__(256) stack_cast_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ x,
+                                                         int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
+    y[e] = __float2bfloat16_rn(x[e]);
+}
+// y[r, j] = bf16( gelu_tanh(g[r, j]) · table[tok[r]·table_ld + col + j] )
+__global__ void __launch_bounds__(256) stack_act_table_kernel(__nv_bfloat16* __restrict__ y,
+                                                              const __nv_bfloat16* __restrict__ g,
+                                                              const __nv_bfloat16* __restrict__ table,
+                                                              const int32_t* __restrict__ tok, int64_t table_ld, int col,
+                                                              int n, int64_t total) {
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / n;
+    const int j = (int)(e % n);
+    y[e] = __float2bfloat16_rn(gelu_tanh(__bfloat162float(g[e])) * __bfloat162float(table[(int64_t)tok[r] * table_ld + col + j]));
+  }
 }
 
 template <typename T>
@@ -203,12 +222,16 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   const int lo = p.a.window > 0 ? max(0, i - p.a.window + 1) : 0;
   const int na = min(p.a.keep_first, lo);
   const int total = na + (i - lo + 1);
+  // this CTA's share of the visible list (all of it unless the keys are split over blockIdx.y)
+  const bool split = NW > 1 && p.split_ws != nullptr;
+  const int begin = split ? (int)blockIdx.y * p.keys_per_split : 0;
+  const int end = split ? min(total, begin + p.keys_per_split) : total;
   float m = -INFINITY, l = 0.f, acc[VR];
 #pragma unroll
   for (int r = 0; r < VR; ++r) acc[r] = 0.f;
-  for (int c0 = wi * 32; c0 < total; c0 += NW * 32) {
+  for (int c0 = begin + wi * 32; c0 < end; c0 += NW * 32) {
     const int idx = c0 + lane;
-    const bool valid = idx < total;
+    const bool valid = idx < end;
     const int j = idx < na ? idx : lo + (idx - na);
     float s = -INFINITY;
     if (valid) {
@@ -233,7 +256,7 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     l = l * corr + warp_sum(pj);
 #pragma unroll
     for (int r = 0; r < VR; ++r) acc[r] *= corr;
-    const int cn = min(32, total - c0);
+    const int cn = min(32, end - c0);
     for (int jj = 0; jj < cn; ++jj) {
       const float pw = __shfl_sync(0xffffffffu, pj, jj);
       const int jr = __shfl_sync(0xffffffffu, j, jj);
@@ -276,6 +299,19 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
         if (d < vdim) acc[r] += o[2 + d] * f;
       }
     }
+    if (split) {   // partial of this split: {max, sum, weighted values}; stack_attn_merge_kernel finishes the pair
+      float* o = p.split_ws + ((size_t)pair * p.nsplit + blockIdx.y) * (2 + vdim);
+      if (lane == 0) {
+        o[0] = mt;
+        o[1] = l;
+      }
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < vdim) o[2 + d] = acc[r];
+      }
+      return;
+    }
   }
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
@@ -284,6 +320,36 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   for (int r = 0; r < VR; ++r) {
     const int d = lane + 32 * r;
     if (d < vdim) orow[d] = cvt<T>(acc[r] / l * gate);
+  }
+}
+
+// one warp per (token, head): merge the splits' partial softmaxes, apply the gate, store
+template <typename T>
+__global__ void __launch_bounds__(128) stack_attn_merge_kernel(const StackAttn p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
+  const int t = (int)(pair / p.a.heads), h = (int)(pair % p.a.heads);
+  if (t >= p.n_tok) return;
+  const int vdim = p.a.vdim;
+  const float* base = p.split_ws + (size_t)pair * p.nsplit * (2 + vdim);
+  float mt = -INFINITY;
+  for (int s = 0; s < p.nsplit; ++s) mt = fmaxf(mt, base[(size_t)s * (2 + vdim)]);
+  float l = 0.f;
+  for (int s = 0; s < p.nsplit; ++s) {
+    const float* o = base + (size_t)s * (2 + vdim);
+    if (o[0] != -INFINITY) l += o[1] * expf(o[0] - mt);
+  }
+  const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  float gate = 1.f;
+  if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
+  T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
+  for (int d = lane; d < vdim; d += 32) {
+    float a = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float* o = base + (size_t)s * (2 + vdim);
+      if (o[0] != -INFINITY) a += o[2 + d] * expf(o[0] - mt);
+    }
+    orow[d] = cvt<T>(a / l * gate);
   }
 }
 
@@ -347,7 +413,30 @@ int launch_stack_rmsnorm(void* y, const float* x, const float* w, const int32_t*
 int launch_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int dim, float eps, float mult,
                          cudaStream_t st) {
   B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
-  B200_CUDA(launch_pdl(stack_rms_add_kernel, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps, mult));
+  B200_CUDA(launch_pdl(stack_rms_add_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps, mult));
+  return B200_OK;
+}
+
+int launch_stack_rms_add_bf16(float* x, const __nv_bfloat16* y, const float* w, int64_t rows, int dim, float eps, float mult,
+                              cudaStream_t st) {
+  B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
+  B200_CUDA(launch_pdl(stack_rms_add_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps,
+                       mult));
+  return B200_OK;
+}
+
+int launch_stack_cast(__nv_bfloat16* y, const float* x, int64_t total, cudaStream_t st) {
+  B200_CHECK_ARG(y && x && total > 0, "stack cast: bad arguments");
+  B200_CUDA(launch_pdl(stack_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, x, total));
+  return B200_OK;
+}
+
+int launch_stack_act_table(__nv_bfloat16* y, const __nv_bfloat16* g, const void* table, const int32_t* tok, int64_t table_ld,
+                           int col, int64_t rows, int n, cudaStream_t st) {
+  B200_CHECK_ARG(y && g && table && tok && rows > 0 && n > 0, "stack act_table: bad arguments");
+  const int64_t total = rows * n;
+  B200_CUDA(launch_pdl(stack_act_table_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, g,
+                       (const __nv_bfloat16*)table, tok, table_ld, col, n, total));
   return B200_OK;
 }
 
@@ -425,7 +514,7 @@ template <typename T, int NW, bool VEC>
 static cudaError_t launch_attn_t(const StackAttn& p, cudaStream_t st) {
   const int64_t pairs = (int64_t)p.n_tok * p.a.heads;
   const int ppb = 4 / NW;
-  const dim3 grid((unsigned)((pairs + ppb - 1) / ppb));
+  const dim3 grid((unsigned)((pairs + ppb - 1) / ppb), (unsigned)((NW > 1 && p.split_ws != nullptr) ? p.nsplit : 1));
   const size_t smem = ((size_t)4 * p.a.dim + (NW > 1 ? (size_t)NW * (2 + p.a.vdim) : 0)) * sizeof(float);
   const int vr = (p.a.vdim + 31) / 32;
   if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1, NW, VEC>, grid, dim3(128), smem, st, false, p);
@@ -439,8 +528,10 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
   int rc = check_attn(p);
   if (rc != B200_OK) return rc;
   B200_CHECK_ARG(p.out != nullptr, "stack attention: null output");
+  B200_CHECK_ARG(p.split_ws == nullptr || (p.nsplit >= 1 && p.keys_per_split > 0 && p.n_tok <= kStackSplitRows),
+                 "stack attention: bad key split");
   // few (token, head) pairs: four warps share one pair's keys
-  const bool wide = (int64_t)p.n_tok * p.a.heads < 4 * 148 * 4;
+  const bool wide = p.split_ws != nullptr || (int64_t)p.n_tok * p.a.heads < 4 * 148 * 4;
   const bool vec = dtype == B200_BF16 && p.a.dim % 8 == 0 && p.k_slot_stride % 8 == 0 &&
                    (reinterpret_cast<uintptr_t>(p.kcache) & 15) == 0;
   if (dtype == B200_F32) {
@@ -452,6 +543,11 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
   } else {
     if (wide) B200_CUDA((launch_attn_t<__nv_bfloat16, 4, false>(p, st)));
     else B200_CUDA((launch_attn_t<__nv_bfloat16, 1, false>(p, st)));
+  }
+  if (p.split_ws != nullptr) {
+    const dim3 grid((unsigned)(((int64_t)p.n_tok * p.a.heads + 3) / 4));
+    if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_attn_merge_kernel<float>, grid, dim3(128), 0, st, false, p));
+    else B200_CUDA(launch_pdl(stack_attn_merge_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, false, p));
   }
   return B200_OK;
 }

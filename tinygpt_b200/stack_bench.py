@@ -1,0 +1,150 @@
+"""Prefill and decode throughput of a layer-stack design (Kozusun) beside the closest Llama-family model of equal size.
+
+`python bench.py --stack-compare` prints ONE JSON line: per size, tokens/s of a prompt pass and of greedy decoding (one
+sequence and eight), for both engines, with random weights of the real shapes.  "Equal size": same width, head counts,
+head size, feed-forward width and vocabulary, and as many Llama layers as the stack model has layer runs, so both read
+the same matrices per token (the stack model adds its gate rows, the token table and the loop's mix-in product).
+
+Timing: CUDA events on the launching stream, synchronised on both sides, warm-up first; a buffer larger than L2 is
+written between timed iterations.
+"""
+from __future__ import annotations
+
+import json
+from typing import Dict, List
+
+import torch
+
+from . import engine, models
+
+SIZES = {
+    # name: width, heads, kv_heads, head size, ff, vocab, layers, (loop start, stop, times), window, kept first, side columns
+    "w2048": dict(width=2048, heads=16, kv_heads=8, dim=128, ff=6144, vocab=65536, layers=6, loop=(0, 2, 2),
+                  window=1024, keep_first=4, side_dim=64),
+    "w3072": dict(width=3072, heads=24, kv_heads=8, dim=128, ff=8192, vocab=65536, layers=6, loop=(0, 2, 2),
+                  window=1024, keep_first=4, side_dim=64),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, vocab=32768, layers=3, loop=(0, 1, 2),
+                  window=1024, keep_first=4, side_dim=64),
+}
+
+
+def stack_spec(name: str, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = SIZES[name]
+    attn = models.AttnSpec(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["dim"] ** -0.5, z["window"], z["keep_first"])
+    lo, hi, times = z["loop"]
+    return models.StackSpec(name="kozusun-" + name, architecture="Kozusun", width=z["width"], vocab=z["vocab"],
+                            layers=tuple(models.StackLayerSpec(attn, z["ff"]) for _ in range(z["layers"])),
+                            loop_start=lo, loop_stop=hi, loop_times=times, embed_scale=8.0, residual_mult=0.3,
+                            norm_eps=1e-5, norm_offset=1.0, side_dim=z["side_dim"], max_ctx=max_ctx, max_slots=max_slots)
+
+
+def llama_spec(name: str, n_layers: int, max_ctx: int) -> models.ModelSpec:
+    z = SIZES[name]
+    return models.ModelSpec("llama-" + name, "llama", z["width"], n_layers, z["heads"], z["kv_heads"], z["dim"], z["ff"],
+                            z["vocab"], 5e5, 1e-5, tie=False, max_ctx=max_ctx)
+
+
+def device_stack_weights(spec: models.StackSpec, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random weights straight in the engine's layout on the device (no host copy of a multi-GB checkpoint)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = spec.width
+
+    def mat(o, i):
+        return (torch.randn(o, i, generator=g, device=device, dtype=torch.float32) * (i ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, centre=0.0):
+        return centre + torch.randn(n, generator=g, device=device, dtype=torch.float32) * 0.05
+
+    w = {"embed": mat(spec.vocab, W), "head": mat(spec.vocab, W), "final_norm": vec(W)}
+    if spec.loop_times > 0:
+        w["mix_in"] = mat(W, 2 * W)
+    if spec.side_dim > 0:
+        w["side_table"] = mat(spec.vocab, spec.side_dim * len(spec.layers))
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.layout(i), f"l{i}."
+        w[p + "norm"] = vec(W)
+        w[p + "w_in"], w[p + "b_in"] = mat(lay.n_in, W), vec(lay.n_in)
+        w[p + "w_out"] = mat(W, lay.k_out)
+        if spec.side_dim > 0:
+            w[p + "side_gate"], w[p + "side_proj"], w[p + "side_norm"] = mat(spec.side_dim, W), mat(W, spec.side_dim), vec(W, 1.0)
+    return w
+
+
+class _Timer:
+    def __init__(self, device):
+        self.device = device
+        self.flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)   # larger than the 126 MB L2
+
+    def run(self, fn, prepare, steps: int, warmup: int) -> float:
+        """Median milliseconds of fn() over `steps` runs after `warmup` runs; prepare() and an L2 flush before each."""
+        times = []
+        for i in range(warmup + steps):
+            prepare()
+            self.flush.fill_(i & 0xff)
+            torch.cuda.synchronize(self.device)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize(self.device)
+            if i >= warmup:
+                times.append(a.elapsed_time(b))
+        times.sort()
+        return times[len(times) // 2]
+
+
+def _measure(eng, is_stack: bool, prompt_len: int, n_decode: int, timer: _Timer, steps: int, warmup: int, vocab: int) -> dict:
+    dev = eng.device
+    g = torch.Generator().manual_seed(1)
+    out = {}
+    for B in (1, 8):
+        ids = torch.randint(0, vocab, (B, prompt_len), generator=g).to(dev)
+
+        def prefill():
+            eng.gen_next_token(ids)
+
+        ms = timer.run(prefill, eng.reset_cache, steps, warmup)
+        out[f"prefill_b{B}_tok_s"] = round(B * prompt_len / ms * 1e3, 1)
+        out[f"prefill_b{B}_ms"] = round(ms, 3)
+
+        def prep():
+            eng.reset_cache()
+            eng.gen_next_token(ids)
+
+        ms = timer.run(lambda: eng.decode(n_decode), prep, steps, warmup)
+        out[f"decode_b{B}_tok_s"] = round(B * n_decode / ms * 1e3, 1)
+        out[f"decode_b{B}_us_per_step"] = round(ms / n_decode * 1e3, 1)
+    return out
+
+
+def compare(sizes: List[str], steps: int = 5, warmup: int = 3, prompt_len: int = 2048, n_decode: int = 32) -> dict:
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    timer = _Timer(dev)
+    max_ctx = prompt_len + n_decode + 8
+    rows = {}
+    for name in sizes:
+        sspec = stack_spec(name, max_ctx)
+        eng = engine.DecodeEngine(sspec, device_stack_weights(sspec, dev))
+        k = _measure(eng, True, prompt_len, n_decode, timer, steps, warmup, sspec.vocab)
+        k["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        lspec = llama_spec(name, len(sspec.runs()), max_ctx)
+        eng = engine.DecodeEngine(lspec, models.synth_weights(lspec, seed=0, device=str(dev), device_generator=True))
+        l = _measure(eng, False, prompt_len, n_decode, timer, steps, warmup, lspec.vocab)
+        l["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        rows[name] = {"kozusun": k, "llama_family": l,
+                      "ratio": {m: round(k[m] / l[m], 3) for m in k if m.endswith("tok_s")}}
+    return {"metric": "stack_compare", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+            "decode_steps": n_decode, "steps": steps, "warmup": warmup, "l2": "flushed between timed iterations",
+            "sizes": rows}
+
+
+def main(sizes: str, steps: int, warmup: int) -> None:
+    names = [s for s in sizes.split(",") if s] if sizes and sizes != "all" else list(SIZES)
+    print(json.dumps(compare(names, steps=steps, warmup=warmup)), flush=True)
