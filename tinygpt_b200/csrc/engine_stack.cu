@@ -62,6 +62,9 @@ struct StackEngine {
   // (gemv.cu / gemv_batch.cu) for steps of up to kMaxBatch rows, the tcgen05 GEMM (gemm.cu) for steps of kGemmRows and
   // more rows; B200_STACK_PLAIN=1 keeps everything on the general kernels
   bool fast = false;
+  // the GEMV kernels wait for their producer themselves (griddepcontrol.wait) after they have filled their weight ring,
+  // so they may be launched ahead of the end of whatever kernel precedes them; B200_NO_PDL=1 turns that off
+  bool pdl = true;
   int num_sms = 148;
   struct Plans {
     GemvPlan in{}, out{}, side_gate{}, side_proj{};
@@ -194,7 +197,7 @@ static int stack_product_in(StackEngine* s, int li, int n_tok, cudaStream_t st) 
     pl.p.y = (__nv_bfloat16*)s->proj;
     pl.p.fbias = L.b_in;
     if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
-    return gemv_launch(pl, st, false);
+    return gemv_launch(pl, st, s->pdl);
   }
   if (s->fast && n_tok >= kGemmRows && gemm_shape_ok(L.n_in, W)) {
     if ((rc = launch_gemm_bf16(s->proj, s->h, L.w_in, n_tok, L.n_in, W, st)) != B200_OK) return rc;
@@ -218,7 +221,7 @@ static int stack_product_out(StackEngine* s, int li, float* x, int n_tok, cudaSt
     pl.p.yf = x;
     pl.p.mult = s->d.residual_mult;
     if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
-    return gemv_launch(pl, st, false);
+    return gemv_launch(pl, st, s->pdl);
   }
   if (s->fast && n_tok >= kGemmRows && gemm_shape_ok(W, L.k_out)) {   // h is free again: it holds the bf16 product
     if ((rc = launch_gemm_bf16(s->h, s->mid, L.w_out, n_tok, W, L.k_out, st)) != B200_OK) return rc;
@@ -245,7 +248,7 @@ static int stack_product_mix(StackEngine* s, const float* cur, float* other, int
       pl.p.yf = other;
       pl.p.mult = 1.f;
       if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
-      return gemv_launch(pl, st, false);
+      return gemv_launch(pl, st, s->pdl);
     }
     if ((rc = launch_gemm_bf16(s->h, s->cat, s->d.mix_in, n_tok, W, 2 * W, st)) != B200_OK) return rc;
     return launch_stack_axpy(other, (const __nv_bfloat16*)s->h, 1.f, false, (int64_t)n_tok * W, st);
@@ -267,7 +270,7 @@ static int stack_product_head(StackEngine* s, int n_rows, cudaStream_t st) {
     pl.p.y = s->logits_bf;
     pl.p.yf = s->logits;
     if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
-    return gemv_launch(pl, st, false);
+    return gemv_launch(pl, st, s->pdl);
   }
   StackGemm g;
   g.a = s->hn; g.lda = d.width; g.k1 = d.width;
@@ -337,7 +340,7 @@ static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_
       GemvPlan pl = s->plans[li].side_gate;
       pl.p.x = xb;
       pl.p.y = raw;
-      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, false)) != B200_OK) return rc;
+      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, s->pdl)) != B200_OK) return rc;
     } else if ((rc = launch_gemm_bf16(raw, xb, L.side_gate, n_tok, sd, W, st)) != B200_OK) {
       return rc;
     }
@@ -348,7 +351,7 @@ static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_
       pl.p.x = sg;
       pl.p.y = xb;          // the rounded copy is not used
       pl.p.yf = s->y;
-      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, false)) != B200_OK) return rc;
+      if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, s->pdl)) != B200_OK) return rc;
       return launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st);
     }
     if ((rc = launch_gemm_bf16(xb, sg, L.side_proj, n_tok, W, sd, st)) != B200_OK) return rc;
@@ -816,7 +819,8 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   e->d.layers = d.n_layers;
   e->V_l = d.vocab;
   e->use_graph = !env_flag("B200_NO_GRAPH", false);
-  e->use_pdl = false;
+  s->pdl = !env_flag("B200_NO_PDL", false);
+  e->use_pdl = s->pdl;
   guard.e = nullptr;
   *out = e;
   return B200_OK;

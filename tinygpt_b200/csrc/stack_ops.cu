@@ -199,8 +199,10 @@ __global__ void __launch_bounds__(128) stack_kv_store_kernel(const StackAttn p) 
 // dealt to the warps 32 at a time and the partial softmaxes merged through shared memory (decode steps: few pairs, long
 // key lists).  The visible keys of a query at position i are the kept first rows [0, min(keep_first, lo)) followed by
 // the window [lo, i], lo = max(0, i − window + 1) (window 0: lo = 0).  A warp walks its share of that list 32 keys at a
-// time: lane j scores key j (fp32 dot, times scale; VEC: 16-byte loads of bf16 rows), the chunk joins an online softmax,
-// then the lanes turn to the value columns (lane + 32·r) and add the chunk's weighted rows.
+// time: lane j scores key j (fp32 dot, times scale), the chunk joins an online softmax, then the lanes turn to the value
+// columns and add the chunk's weighted rows: column lane + 32·r of one row at a time, or — VEC: bf16, key size a multiple
+// of 8, value size 8 … 256 and a power of two — 16-byte loads throughout, vdim/8 lanes per value row and 256/vdim rows
+// per pass (the groups' sums meet in a butterfly after the walk).
 template <typename T, int VR, int NW, bool VEC>
 __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   extern __shared__ float smem_f[];
@@ -226,9 +228,25 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   const bool split = NW > 1 && p.split_ws != nullptr;
   const int begin = split ? (int)blockIdx.y * p.keys_per_split : 0;
   const int end = split ? min(total, begin + p.keys_per_split) : total;
-  float m = -INFINITY, l = 0.f, acc[VR];
+  constexpr int NA = VEC ? 8 : VR;
+  float m = -INFINITY, l = 0.f, acc[NA];
 #pragma unroll
-  for (int r = 0; r < VR; ++r) acc[r] = 0.f;
+  for (int r = 0; r < NA; ++r) acc[r] = 0.f;
+  // the value columns a lane owns once the walk is over, as fn(column, accumulator)
+  auto cols = [&](auto&& fn) {
+    if constexpr (VEC) {
+      if (lane < (vdim >> 3)) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) fn(lane * 8 + e, acc[e]);
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < VR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < vdim) fn(d, acc[r]);
+      }
+    }
+  };
   for (int c0 = begin + wi * 32; c0 < end; c0 += NW * 32) {
     const int idx = c0 + lane;
     const bool valid = idx < end;
@@ -255,19 +273,41 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     const float pj = valid ? expf(s - mn) : 0.f;
     l = l * corr + warp_sum(pj);
 #pragma unroll
-    for (int r = 0; r < VR; ++r) acc[r] *= corr;
+    for (int r = 0; r < NA; ++r) acc[r] *= corr;
     const int cn = min(32, end - c0);
-    for (int jj = 0; jj < cn; ++jj) {
-      const float pw = __shfl_sync(0xffffffffu, pj, jj);
-      const int jr = __shfl_sync(0xffffffffu, j, jj);
-      const T* vr = vb + (int64_t)jr * vrs;
+    if constexpr (VEC) {
+      const int G = vdim >> 3, KP = 32 / G;   // lanes per value row, rows per pass
+      const int grp = lane / G, gl = lane % G;
+      for (int jj = 0; jj < cn; jj += KP) {
+        const int src = jj + grp;             // < 32: jj is a multiple of KP and grp < KP
+        const float pw = __shfl_sync(0xffffffffu, pj, src);
+        const int jr = __shfl_sync(0xffffffffu, j, src);
+        if (src < cn) {
+          float vf[8];
+          unpack8(*reinterpret_cast<const uint4*>(vb + (int64_t)jr * vrs + gl * 8), vf);
 #pragma unroll
-      for (int r = 0; r < VR; ++r) {
-        const int d = lane + 32 * r;
-        if (d < vdim) acc[r] = fmaf(pw, ldf<T>(vr + d), acc[r]);
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(pw, vf[e], acc[e]);
+        }
+      }
+    } else {
+      for (int jj = 0; jj < cn; ++jj) {
+        const float pw = __shfl_sync(0xffffffffu, pj, jj);
+        const int jr = __shfl_sync(0xffffffffu, j, jj);
+        const T* vr = vb + (int64_t)jr * vrs;
+#pragma unroll
+        for (int r = 0; r < VR; ++r) {
+          const int d = lane + 32 * r;
+          if (d < vdim) acc[r] = fmaf(pw, ldf<T>(vr + d), acc[r]);
+        }
       }
     }
     m = mn;
+  }
+  if constexpr (VEC) {   // the row groups' partial sums of a column meet
+    for (int off = vdim >> 3; off < 32; off <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+    }
   }
   if constexpr (NW > 1) {
     // merge the warps' partial softmaxes: scratch [NW][2 + vdim] behind the four query vectors
@@ -277,27 +317,19 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
       mine[0] = m;
       mine[1] = l;
     }
-#pragma unroll
-    for (int r = 0; r < VR; ++r) {
-      const int d = lane + 32 * r;
-      if (d < vdim) mine[2 + d] = acc[r];
-    }
+    cols([&](int d, float& a) { mine[2 + d] = a; });
     __syncthreads();
     if (wi != 0) return;
     float mt = -INFINITY;
     for (int w = 0; w < NW; ++w) mt = fmaxf(mt, sc[w * (2 + vdim)]);
     l = 0.f;
 #pragma unroll
-    for (int r = 0; r < VR; ++r) acc[r] = 0.f;
+    for (int r = 0; r < NA; ++r) acc[r] = 0.f;
     for (int w = 0; w < NW; ++w) {
       const float* o = sc + w * (2 + vdim);
       const float f = o[0] == -INFINITY ? 0.f : expf(o[0] - mt);
       l += o[1] * f;
-#pragma unroll
-      for (int r = 0; r < VR; ++r) {
-        const int d = lane + 32 * r;
-        if (d < vdim) acc[r] += o[2 + d] * f;
-      }
+      cols([&](int d, float& a) { a += o[2 + d] * f; });
     }
     if (split) {   // partial of this split: {max, sum, weighted values}; stack_attn_merge_kernel finishes the pair
       float* o = p.split_ws + ((size_t)pair * p.nsplit + blockIdx.y) * (2 + vdim);
@@ -305,22 +337,15 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
         o[0] = mt;
         o[1] = l;
       }
-#pragma unroll
-      for (int r = 0; r < VR; ++r) {
-        const int d = lane + 32 * r;
-        if (d < vdim) o[2 + d] = acc[r];
-      }
+      cols([&](int d, float& a) { o[2 + d] = a; });
       return;
     }
   }
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
   T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
-#pragma unroll
-  for (int r = 0; r < VR; ++r) {
-    const int d = lane + 32 * r;
-    if (d < vdim) orow[d] = cvt<T>(acc[r] / l * gate);
-  }
+  const float fin = gate / l;
+  cols([&](int d, float& a) { orow[d] = cvt<T>(a * fin); });
 }
 
 // one warp per (token, head): merge the splits' partial softmaxes, apply the gate, store
@@ -332,24 +357,29 @@ __global__ void __launch_bounds__(128) stack_attn_merge_kernel(const StackAttn p
   if (t >= p.n_tok) return;
   const int vdim = p.a.vdim;
   const float* base = p.split_ws + (size_t)pair * p.nsplit * (2 + vdim);
-  float mt = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s) mt = fmaxf(mt, base[(size_t)s * (2 + vdim)]);
-  float l = 0.f;
-  for (int s = 0; s < p.nsplit; ++s) {
-    const float* o = base + (size_t)s * (2 + vdim);
-    if (o[0] != -INFINITY) l += o[1] * expf(o[0] - mt);
-  }
+  // lanes over splits (nsplit <= 64: two per lane) for the maxima and the sums …
+  const int s0 = lane, s1 = lane + 32;
+  const float m0 = s0 < p.nsplit ? base[(size_t)s0 * (2 + vdim)] : -INFINITY;
+  const float m1 = s1 < p.nsplit ? base[(size_t)s1 * (2 + vdim)] : -INFINITY;
+  const float l0 = s0 < p.nsplit ? base[(size_t)s0 * (2 + vdim) + 1] : 0.f;
+  const float l1 = s1 < p.nsplit ? base[(size_t)s1 * (2 + vdim) + 1] : 0.f;
+  const float mt = warp_max(fmaxf(m0, m1));
+  const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - mt), f1 = m1 == -INFINITY ? 0.f : expf(m1 - mt);
+  const float l = warp_sum(l0 * f0 + l1 * f1);
   const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
+  const float fin = gate / l;
   T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
-  for (int d = lane; d < vdim; d += 32) {
+  // … then lanes over value columns, the splits' weights handed round by shuffle (independent loads per split)
+  for (int d0 = 0; d0 < vdim; d0 += 32) {
+    const int d = d0 + lane;
     float a = 0.f;
     for (int s = 0; s < p.nsplit; ++s) {
-      const float* o = base + (size_t)s * (2 + vdim);
-      if (o[0] != -INFINITY) a += o[2 + d] * expf(o[0] - mt);
+      const float f = __shfl_sync(0xffffffffu, s < 32 ? f0 : f1, s & 31);
+      if (d < vdim && f != 0.f) a = fmaf(base[(size_t)s * (2 + vdim) + 2 + d], f, a);
     }
-    orow[d] = cvt<T>(a / l * gate);
+    if (d < vdim) orow[d] = cvt<T>(a * fin);
   }
 }
 
@@ -532,8 +562,10 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
                  "stack attention: bad key split");
   // few (token, head) pairs: four warps share one pair's keys
   const bool wide = p.split_ws != nullptr || (int64_t)p.n_tok * p.a.heads < 4 * 148 * 4;
-  const bool vec = dtype == B200_BF16 && p.a.dim % 8 == 0 && p.k_slot_stride % 8 == 0 &&
-                   (reinterpret_cast<uintptr_t>(p.kcache) & 15) == 0;
+  const int vd = p.a.vdim;
+  const bool vec = dtype == B200_BF16 && p.a.dim % 8 == 0 && vd >= 8 && vd <= 256 && (vd & (vd - 1)) == 0 &&
+                   p.k_slot_stride % 8 == 0 && p.v_slot_stride % 8 == 0 &&
+                   ((reinterpret_cast<uintptr_t>(p.kcache) | reinterpret_cast<uintptr_t>(p.vcache)) & 15) == 0;
   if (dtype == B200_F32) {
     if (wide) B200_CUDA((launch_attn_t<float, 4, false>(p, st)));
     else B200_CUDA((launch_attn_t<float, 1, false>(p, st)));
