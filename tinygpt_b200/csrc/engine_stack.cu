@@ -77,9 +77,10 @@ struct StackEngine {
   };
   std::vector<Seg> segs;
   float* attn_ws = nullptr;       // split-key partials of decode steps
+  unsigned int* attn_tickets = nullptr;
   int max_heads = 1, max_vdim = 1;
   std::vector<Plans> plans;
-  GemvPlan p_mix{}, p_head{};
+  GemvPlan p_mix{}, p_head{}, p_head_f{};   // p_head_f: final norm fused (rows in stream order)
   bool ok_mix = false, ok_head = false;
   __nv_bfloat16* cat = nullptr;   // bf16 [x | x0] rows for the mix-in product
   // greedy decode steps as CUDA graphs, one per number of rows (row → slot goes through row_slot on the device, so a
@@ -159,6 +160,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_meta = take((3 * T + rows + 2 * (size_t)d.max_slots) * 4);
   const size_t o_cat = take(d.mix_in != nullptr && s->dtype == B200_BF16 ? T * 2 * W * 2 : 0);
   const size_t o_aws = take((size_t)kStackSplitRows * s->max_heads * kStackMaxSplits * (2 + s->max_vdim) * 4);
+  const size_t o_tick = take((size_t)kStackSplitRows * s->max_heads * 4);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->ws_tok = tok;
@@ -181,24 +183,31 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->m_upd = s->m_want + rows;
   s->cat = (__nv_bfloat16*)(s->ws + o_cat);
   s->attn_ws = (float*)(s->ws + o_aws);
+  s->attn_tickets = (unsigned int*)(s->ws + o_tick);
   return B200_OK;
 }
 
 static inline bool gemm_shape_ok(int64_t N, int64_t K) { return N % 8 == 0 && K % 8 == 0 && K >= 64; }
 
-// proj = h·w_inᵀ + b_in
-static int stack_product_in(StackEngine* s, int li, int n_tok, cudaStream_t st) {
+// proj = rmsnorm(x)·(offset + w) · w_inᵀ + b_in
+static int stack_product_in(StackEngine* s, int li, const float* x, int n_tok, cudaStream_t st) {
   const b200_stack_layer& L = s->layers[li];
-  const int W = s->d.width;
+  const b200_stack_desc& d = s->d;
+  const int W = d.width;
   int rc;
-  if (s->fast && n_tok <= kMaxBatch && s->plans[li].ok_in) {
+  if (s->fast && n_tok <= kMaxBatch && s->plans[li].ok_in) {   // the norm is the GEMV's prologue
     GemvPlan pl = s->plans[li].in;
-    pl.p.x = (const __nv_bfloat16*)s->h;
+    pl.p.xf = x;
+    pl.p.fnorm_w = L.norm;
+    pl.p.norm_offset = d.norm_offset;
+    pl.p.eps = d.norm_eps;
     pl.p.y = (__nv_bfloat16*)s->proj;
     pl.p.fbias = L.b_in;
     if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK) return rc;
     return gemv_launch(pl, st, s->pdl);
   }
+  if ((rc = launch_stack_rmsnorm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, s->dtype, st)) != B200_OK)
+    return rc;
   if (s->fast && n_tok >= kGemmRows && gemm_shape_ok(L.n_in, W)) {
     if ((rc = launch_gemm_bf16(s->proj, s->h, L.w_in, n_tok, L.n_in, W, st)) != B200_OK) return rc;
     return L.b_in ? launch_stack_bias_add((__nv_bfloat16*)s->proj, L.b_in, n_tok, L.n_in, st) : B200_OK;
@@ -260,10 +269,24 @@ static int stack_product_mix(StackEngine* s, const float* cur, float* other, int
   return launch_stack_gemm(g, s->dtype, st);
 }
 
-// logits (fp32) and logits_bf (bf16) = hn·headᵀ
-static int stack_product_head(StackEngine* s, int n_rows, cudaStream_t st) {
+// logits (fp32) and logits_bf (bf16) = rmsnorm(x[rows])·(offset + w) · headᵀ; rows == null: the stream's rows in order
+static int stack_product_head(StackEngine* s, const float* x, const int32_t* rows, int n_rows, cudaStream_t st) {
   const b200_stack_desc& d = s->d;
   int rc;
+  if (s->fast && n_rows <= kMaxBatch && s->ok_head && rows == nullptr) {   // the final norm is the GEMV's prologue
+    GemvPlan pl = s->p_head_f;
+    pl.p.xf = x;
+    pl.p.fnorm_w = d.final_norm;
+    pl.p.norm_offset = d.norm_offset;
+    pl.p.eps = d.norm_eps;
+    pl.p.y = s->logits_bf;
+    pl.p.yf = s->logits;
+    if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
+    return gemv_launch(pl, st, s->pdl);
+  }
+  if ((rc = launch_stack_rmsnorm(s->hn, x, d.final_norm, rows, n_rows, d.width, d.norm_eps, d.norm_offset, s->dtype, st)) !=
+      B200_OK)
+    return rc;
   if (s->fast && n_rows <= kMaxBatch && s->ok_head) {
     GemvPlan pl = s->p_head;
     pl.p.x = (const __nv_bfloat16*)s->hn;
@@ -299,6 +322,7 @@ static int stack_attention(StackEngine* s, const StackAttn& a, const b200_stack_
     const int nsplit = std::min(kStackMaxSplits, (kmax + kStackSplitKeys - 1) / kStackSplitKeys);
     if (count <= kStackSplitRows && nsplit > 1) {
       q.split_ws = s->attn_ws;
+      q.split_tickets = s->attn_tickets;
       q.nsplit = nsplit;
       q.keys_per_split = ((kmax + nsplit - 1) / nsplit + 31) / 32 * 32;
     }
@@ -335,17 +359,21 @@ static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_
   if (gemv || gemm) {
     // bf16 operand of the stream in h, the gate product in proj (both are free here), the gated table row in sg
     __nv_bfloat16 *xb = (__nv_bfloat16*)s->h, *raw = (__nv_bfloat16*)s->proj, *sg = (__nv_bfloat16*)s->sg;
-    if ((rc = launch_stack_cast(xb, cur, (int64_t)n_tok * W, st)) != B200_OK) return rc;
-    if (gemv) {
+    if (gemv) {   // one launch: fp32 stream in, gelu(·)·table row out
       GemvPlan pl = s->plans[li].side_gate;
-      pl.p.x = xb;
-      pl.p.y = raw;
+      pl.p.xf = cur;
+      pl.p.y = sg;
+      pl.p.table = (const __nv_bfloat16*)d.side_table;
+      pl.p.tok = s->m_tok;
+      pl.p.table_ld = d.side_stride;
+      pl.p.table_col = L.side_col;
       if ((rc = gemv_plan_set_batch(&pl, n_tok)) != B200_OK || (rc = gemv_launch(pl, st, s->pdl)) != B200_OK) return rc;
-    } else if ((rc = launch_gemm_bf16(raw, xb, L.side_gate, n_tok, sd, W, st)) != B200_OK) {
-      return rc;
+    } else {
+      if ((rc = launch_stack_cast(xb, cur, (int64_t)n_tok * W, st)) != B200_OK) return rc;
+      if ((rc = launch_gemm_bf16(raw, xb, L.side_gate, n_tok, sd, W, st)) != B200_OK) return rc;
+      if ((rc = launch_stack_act_table(sg, raw, d.side_table, s->m_tok, d.side_stride, L.side_col, n_tok, sd, st)) != B200_OK)
+        return rc;
     }
-    if ((rc = launch_stack_act_table(sg, raw, d.side_table, s->m_tok, d.side_stride, L.side_col, n_tok, sd, st)) != B200_OK)
-      return rc;
     if (gemv) {
       GemvPlan pl = s->plans[li].side_proj;
       pl.p.x = sg;
@@ -372,7 +400,8 @@ static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_
 }
 
 // One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
-static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
+// rows_in_order: m_want is 0 … n_rows-1 (decode steps), so the head may read the stream directly.
+static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bool rows_in_order = false) {
   StackEngine* s = e->stack;
   const b200_stack_desc& d = s->d;
   const int W = d.width, dt = s->dtype;
@@ -386,9 +415,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
       if ((rc = stack_product_mix(s, cur, other, n_tok, st)) != B200_OK) return rc;
       std::swap(cur, other);
     }
-    if ((rc = launch_stack_rmsnorm(s->h, cur, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, dt, st)) != B200_OK)
-      return rc;
-    if ((rc = stack_product_in(s, s->run_layer[r], n_tok, st)) != B200_OK) return rc;
+    if ((rc = stack_product_in(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
     StackAttn a;
     a.a = L.attn;
     a.proj = s->proj; a.ld_proj = L.n_in;
@@ -412,12 +439,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st) {
     if ((rc = stack_product_out(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
     if (L.side_gate != nullptr && (rc = stack_side(s, s->run_layer[r], cur, n_tok, st)) != B200_OK) return rc;
   }
-  if (n_rows > 0) {
-    if ((rc = launch_stack_rmsnorm(s->hn, cur, d.final_norm, s->m_want, n_rows, W, d.norm_eps, d.norm_offset, dt, st)) !=
-        B200_OK)
-      return rc;
-    if ((rc = stack_product_head(s, n_rows, st)) != B200_OK) return rc;
-  }
+  if (n_rows > 0 && (rc = stack_product_head(s, cur, rows_in_order ? nullptr : s->m_want, n_rows, st)) != B200_OK) return rc;
   return B200_OK;
 }
 
@@ -585,7 +607,7 @@ static int stack_decode_step(b200_engine* e, int B, cudaStream_t st) {
   B200_CUDA(launch_pdl(stack_meta_decode_kernel, dim3((B + 63) / 64), dim3(64), 0, st, false, (const int*)s->row_slot, B,
                        s->pos_dev, (const int64_t*)s->cur_tok, s->m_tok, s->m_slot, s->m_pos, s->m_want));
   s->segs.clear();
-  if ((rc = stack_pass(e, B, B, st)) != B200_OK) return rc;
+  if ((rc = stack_pass(e, B, B, st, true)) != B200_OK) return rc;
   return stack_publish(e, 0, s->active, st);
 }
 
@@ -772,20 +794,21 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   if (s->fast) {
     if ((rc = gemv_setup_attributes()) != B200_OK || (rc = gemv_batch_setup_attributes()) != B200_OK) return rc;
     // a plan that cannot be made (k not a multiple of 8, an unaligned matrix) leaves that product on the general kernel
-    auto plan = [&](GemvPlan* pl, const void* w, int64_t n, int64_t k, int epi) {
+    auto plan = [&](GemvPlan* pl, const void* w, int64_t n, int64_t k, int epi, int pro = PRO_PLAIN) {
       if (k % 8 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
-      return gemv_make_plan(pl, w, n, n, k, 1, PRO_PLAIN, epi, s->num_sms) == B200_OK;
+      return gemv_make_plan(pl, w, n, n, k, 1, pro, epi, s->num_sms) == B200_OK;
     };
     for (int l = 0; l < d.n_layers; ++l) {
       const b200_stack_layer& L = s->layers[l];
-      s->plans[l].ok_in = plan(&s->plans[l].in, L.w_in, L.n_in, d.width, EPI_BIAS_F32);
+      s->plans[l].ok_in = plan(&s->plans[l].in, L.w_in, L.n_in, d.width, EPI_BIAS_F32, PRO_F32);
       s->plans[l].ok_out = plan(&s->plans[l].out, L.w_out, d.width, L.k_out, EPI_RESID_F32);
       s->plans[l].ok_side = L.side_gate != nullptr &&
-                            plan(&s->plans[l].side_gate, L.side_gate, d.side_dim, d.width, EPI_BIAS_F32) &&
+                            plan(&s->plans[l].side_gate, L.side_gate, d.side_dim, d.width, EPI_ACT_TABLE, PRO_F32) &&
                             plan(&s->plans[l].side_proj, L.side_proj, d.width, d.side_dim, EPI_BIAS_F32);
     }
     if (d.mix_in) s->ok_mix = plan(&s->p_mix, d.mix_in, d.width, 2 * (int64_t)d.width, EPI_RESID_F32);
-    s->ok_head = plan(&s->p_head, d.head, d.vocab, d.width, EPI_BIAS_F32);
+    s->ok_head = plan(&s->p_head, d.head, d.vocab, d.width, EPI_BIAS_F32) &&
+                 plan(&s->p_head_f, d.head, d.vocab, d.width, EPI_BIAS_F32, PRO_F32);
   }
   const size_t kb = align_up(s->k_slot * d.max_slots * s->esz, 256), vb = align_up(s->v_slot * d.max_slots * s->esz, 256);
   B200_CUDA(cudaMalloc((void**)&s->cache, kb + vb));

@@ -109,7 +109,7 @@ gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap)
   // Everything that does not depend on the producer kernel is fetched BEFORE griddepcontrol.wait: the RMSNorm weight,
   // the bias of this CTA's first row block.
   uint4 wn[kMaxHoist];
-  if constexpr (PRO != PRO_PLAIN) {
+  if constexpr (PRO != PRO_PLAIN && PRO != PRO_F32) {
     const uint4* wg = reinterpret_cast<const uint4*>(p.norm_w);
 #pragma unroll
     for (int j = 0; j < kMaxHoist; ++j) {
@@ -135,7 +135,41 @@ gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap)
     c0 = clock64();   // SM cycles from here: slots 4-7 = first stage landed, first row block summed / stored, last stored
   }
 
-  if constexpr (PRO == PRO_PLAIN) {
+  if constexpr (PRO == PRO_F32) {
+    // fp32 operand (the stack models' residual stream), optionally RMS-normalised with weight (offset + w): fp32
+    // throughout, one rounding to bf16 on the way into shared memory
+    const float4* xg = reinterpret_cast<const float4*>(p.xf);   // k is a multiple of 8, the vector 16-byte aligned
+    const int nq = p.k >> 2, nq_pad = p.k_pad >> 2;
+    float inv = 1.f;
+    if (p.fnorm_w != nullptr) {
+      float ss = 0.f;
+      for (int i = ctid; i < nq; i += kConsumers) {
+        const float4 v = xg[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) red[warp] = ss;
+      named_bar_sync(1, kConsumers);
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < kNW; ++w) tot += red[w];
+      inv = 1.f / sqrtf(tot / (float)p.k + p.eps);
+    }
+    for (int i = ctid; i < nq_pad; i += kConsumers) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f), w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (i < nq) {
+        v = xg[i];
+        if (p.fnorm_w != nullptr) {
+          w4 = reinterpret_cast<const float4*>(p.fnorm_w)[i];
+          w4.x += p.norm_offset; w4.y += p.norm_offset; w4.z += p.norm_offset; w4.w += p.norm_offset;
+        }
+      }
+      uint2 o;   // with a norm: x·inv·(offset + w); without: inv = 1 and w4 = 1 leave x as it is
+      o.x = pack2(v.x * inv * w4.x, v.y * inv * w4.y);
+      o.y = pack2(v.z * inv * w4.z, v.w * inv * w4.w);
+      reinterpret_cast<uint2*>(xs)[i] = o;
+    }
+  } else if constexpr (PRO == PRO_PLAIN) {
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
     uint4* xv = reinterpret_cast<uint4*>(xs);
     for (int i = ctid; i < nvec_pad; i += kConsumers) xv[i] = (i < nvec) ? ldx(xg + i) : make_uint4(0, 0, 0, 0);
@@ -362,6 +396,10 @@ gemv_stream_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap)
         p.y[row] = f_to_bf16(v);
       } else if constexpr (EPI == EPI_RESID_F32) {
         p.yf[row] += p.mult * a0;
+      } else if constexpr (EPI == EPI_ACT_TABLE) {
+        const float z = a0;
+        const float gl = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        p.y[row] = f_to_bf16(gl * bf16_to_f(p.table[(long long)p.tok[0] * p.table_ld + p.table_col + row]));
       } else {  // EPI_TP_PUSH: one 8-byte {value, tag} store per rank, no fence needed
         const uint2 pk = make_uint2(__float_as_uint(a0), tp_tag);
         for (int q = 0; q < p.tp_world; ++q) st_volatile_u2(p.tp_push[q] + row, pk);
@@ -397,6 +435,8 @@ KernelFn pick_kernel(int nseg, int pro, int epi) {
   B200_PICK(PRO_RMSNORM, EPI_PLAIN)
   B200_PICK(PRO_PLAIN, EPI_BIAS_F32)
   B200_PICK(PRO_PLAIN, EPI_RESID_F32)
+  B200_PICK(PRO_F32, EPI_BIAS_F32)
+  B200_PICK(PRO_F32, EPI_ACT_TABLE)
   B200_PICK(PRO_TP_RMSNORM, EPI_PLAIN)
 #undef B200_PICK
   return nullptr;
@@ -420,7 +460,7 @@ int gemv_setup_attributes() {
     const int rpws[3] = {1, 2, 4};
     for (int rpw : rpws)
       for (int nseg = 1; nseg <= 2; ++nseg)
-        for (int pro = 0; pro < 3; ++pro)
+        for (int pro = 0; pro < kGemvProCount; ++pro)
           for (int epi = 0; epi < kGemvEpiCount; ++epi) {
             KernelFn f = pick(rpw, nseg, pro, epi);
             if (!f) continue;
@@ -528,7 +568,7 @@ int gemv_make_plan(GemvPlan* plan, const void* W, int64_t rows_total, int64_t n,
 
 int gemv_plan_set_batch(GemvPlan* plan, int B) {
   B200_CHECK_ARG(B >= 1 && B <= kMaxBatch, "gemv: batch %d out of range (1 … %d)", B, kMaxBatch);
-  B200_CHECK_ARG((plan->pro == PRO_PLAIN || plan->pro == PRO_RMSNORM) && plan->epi != EPI_TP_PUSH,
+  B200_CHECK_ARG((plan->pro == PRO_PLAIN || plan->pro == PRO_RMSNORM || plan->pro == PRO_F32) && plan->epi != EPI_TP_PUSH,
                  "gemv: batched decode is single-GPU only");
   plan->batch = B;
   plan->p.batch = B;

@@ -8,7 +8,10 @@ namespace b200 {
 //   PRO_PLAIN       x is read as is
 //   PRO_RMSNORM     x ← bf16(x * rsqrt(mean(x²)+eps) * w)              (fused input/post-attention/final RMSNorm)
 //   PRO_TP_RMSNORM  h ← bf16(residual + bf16(Σ_r partial_r)); x ← rmsnorm(h); CTA 0 stores h  (tensor parallel)
-enum GemvPro : int { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_TP_RMSNORM = 2 };
+//   PRO_F32         x is an fp32 vector xf (stack models: the residual stream), rounded to bf16 once while it is staged;
+//                   with fnorm_w:  x ← bf16(xf · rsqrt(mean(xf²)+eps) · (norm_offset + fnorm_w)), all in fp32
+enum GemvPro : int { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_TP_RMSNORM = 2, PRO_F32 = 3 };
+constexpr int kGemvProCount = 4;
 // Epilogue: what happens to the fp32 row sums.
 //   EPI_PLAIN     y = bf16(acc); with bias: y = bf16(y + bias)         (reference: second rounding, 3-D Linear input)
 //   EPI_RESIDUAL  y = bf16(residual + bf16(acc))                        (o_proj / down_proj + DecoderLayer add)
@@ -16,9 +19,10 @@ enum GemvPro : int { PRO_PLAIN = 0, PRO_RMSNORM = 1, PRO_TP_RMSNORM = 2 };
 //   EPI_TP_PUSH   fp32 acc stored into every tensor-parallel peer's exchange window + arrival flag
 //   EPI_BIAS_F32  y = bf16(acc + fbias)                                 (stack models: fp32 bias, one rounding)
 //   EPI_RESID_F32 yf += mult · acc                                      (stack models: fp32 residual stream)
+//   EPI_ACT_TABLE y = bf16(gelu_tanh(acc) · table[tok·table_ld + table_col + row])   (stack models: gated token table)
 enum GemvEpi : int { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_TP_PUSH = 3, EPI_BIAS_F32 = 4,
-                     EPI_RESID_F32 = 5 };
-constexpr int kGemvEpiCount = 6;
+                     EPI_RESID_F32 = 5, EPI_ACT_TABLE = 6 };
+constexpr int kGemvEpiCount = 7;
 
 constexpr int kMaxTpWorld = 8;
 constexpr int kMaxBatch = 8;   // sequences one batched decode step serves (gemv_batch.cu: W streamed once for all of them)
@@ -45,6 +49,13 @@ struct GemvParams {
   const float* fbias;             // EPI_BIAS_F32: [n] or null
   float* yf;                      // EPI_RESID_F32: [n] fp32 stream the scaled row sums are added to
   float mult;                     // EPI_RESID_F32
+  const float* xf;                // PRO_F32: [k] fp32 activation (sequence b at b·x_stride)
+  const float* fnorm_w;           // PRO_F32: [k] fp32 norm weight or null (no norm)
+  float norm_offset;              // PRO_F32: the norm multiplies by (norm_offset + fnorm_w)
+  const __nv_bfloat16* table;     // EPI_ACT_TABLE: [vocab, table_ld]
+  const int32_t* tok;             // EPI_ACT_TABLE: token of sequence b at tok[b]
+  long long table_ld;
+  int table_col;
   // batched decode (gemv_batch.cu): `batch` sequences, x / residual / y of sequence b at b·stride elements
   int batch;                      // 0 or 1: the single-sequence kernels
   int x_stride, y_stride;         // = k, n (residual uses y_stride)

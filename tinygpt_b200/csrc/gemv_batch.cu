@@ -57,9 +57,9 @@ gemv_batch_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) 
   constexpr int MT = (kRowsStage + 15) / 16;        // m16 tiles
   constexpr bool kHalfTile = kRowsStage == 8;       // rows 8-15 of the only tile do not exist: a1 = a3 = 0
   constexpr int kSliceK = KB * 32;                  // k-elements of a stage one warp owns
-  static_assert(PRO == PRO_PLAIN || PRO == PRO_RMSNORM, "single-GPU prologues only");
+  static_assert(PRO == PRO_PLAIN || PRO == PRO_RMSNORM || PRO == PRO_F32, "single-GPU prologues only");
   static_assert(EPI == EPI_PLAIN || EPI == EPI_RESIDUAL || EPI == EPI_SILU_MUL || EPI == EPI_BIAS_F32 ||
-                    EPI == EPI_RESID_F32,
+                    EPI == EPI_RESID_F32 || EPI == EPI_ACT_TABLE,
                 "single-GPU epilogues only");
 
   const int nb = p.batch;
@@ -138,7 +138,64 @@ gemv_batch_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) 
   }
 
   // ---- stage the activation vectors
-  if constexpr (PRO == PRO_PLAIN) {
+  if constexpr (PRO == PRO_F32) {
+    // fp32 operands (the stack models' residual stream), optionally RMS-normalised with weight (offset + w): fp32
+    // throughout, one rounding to bf16 on the way into shared memory; all consumer threads share every sequence
+    // (k is a multiple of 8 and the rows are 16-byte aligned: float4 loads, the sequences side by side in registers)
+    const int nq = p.k >> 2, nq_pad = p.k_pad >> 2;
+    float inv[kMaxBatch];
+#pragma unroll
+    for (int b = 0; b < kMaxBatch; ++b) inv[b] = 1.f;
+    if (p.fnorm_w != nullptr) {
+      float ss[kMaxBatch];
+#pragma unroll
+      for (int b = 0; b < kMaxBatch; ++b) ss[b] = 0.f;
+      for (int i = ctid; i < nq; i += kConsumers) {
+#pragma unroll
+        for (int b = 0; b < kMaxBatch; ++b) {
+          if (b < nb) {
+            const float4 v = reinterpret_cast<const float4*>(p.xf + (size_t)b * p.x_stride)[i];
+            ss[b] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < kMaxBatch; ++b) {
+        if (b < nb) {
+          const float t = warp_sum(ss[b]);
+          if (lane == 0) red[b * kNW + warp] = t;
+        }
+      }
+      named_bar_sync(1, kConsumers);
+#pragma unroll
+      for (int b = 0; b < kMaxBatch; ++b) {
+        if (b < nb) {
+          float tot = 0.f;
+#pragma unroll
+          for (int w = 0; w < kNW; ++w) tot += red[b * kNW + w];
+          inv[b] = 1.f / sqrtf(tot / (float)p.k + p.eps);
+        }
+      }
+    }
+    for (int i = ctid; i < nq_pad; i += kConsumers) {
+      float4 w4 = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (p.fnorm_w != nullptr && i < nq) {
+        w4 = reinterpret_cast<const float4*>(p.fnorm_w)[i];
+        w4.x += p.norm_offset; w4.y += p.norm_offset; w4.z += p.norm_offset; w4.w += p.norm_offset;
+      }
+#pragma unroll
+      for (int b = 0; b < kMaxBatch; ++b) {
+        if (b < nb) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (i < nq) v = reinterpret_cast<const float4*>(p.xf + (size_t)b * p.x_stride)[i];
+          uint2 o;   // with a norm: x·inv·(offset + w); without: inv = 1 and w4 = 1 leave x as it is
+          o.x = pack2(v.x * inv[b] * w4.x, v.y * inv[b] * w4.y);
+          o.y = pack2(v.z * inv[b] * w4.z, v.w * inv[b] * w4.w);
+          reinterpret_cast<uint2*>(xs + (size_t)b * xstride)[i] = o;
+        }
+      }
+    }
+  } else if constexpr (PRO == PRO_PLAIN) {
     // vector index outside, sequence inside and unrolled: up to 8 independent 16-byte loads in flight per thread (one L2
     // round trip per pass, not one per sequence)
     for (int i = ctid; i < nvec_pad; i += kConsumers) {
@@ -307,6 +364,10 @@ gemv_batch_kernel(const GemvParams p, const __grid_constant__ CUtensorMap tmap) 
         y[row] = f_to_bf16(v);
       } else if constexpr (EPI == EPI_RESID_F32) {
         p.yf[(size_t)it_b * p.y_stride + row] += p.mult * a[0];
+      } else if constexpr (EPI == EPI_ACT_TABLE) {
+        const float z = a[0];
+        const float gl = 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        y[row] = f_to_bf16(gl * bf16_to_f(p.table[(long long)p.tok[it_b] * p.table_ld + p.table_col + row]));
       } else {  // EPI_SILU_MUL
         const float gt = round_bf16(a[0]);
         const __nv_bfloat16 sg = f_to_bf16(gt / (1.f + expf(-gt)));
@@ -328,6 +389,8 @@ KernelFn pick_r(int nseg, int pro, int epi) {
   if (pro == PRO_PLAIN && epi == EPI_RESIDUAL) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_RESIDUAL>;
   if (pro == PRO_PLAIN && epi == EPI_BIAS_F32) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_BIAS_F32>;
   if (pro == PRO_PLAIN && epi == EPI_RESID_F32) return gemv_batch_kernel<RPW, 1, PRO_PLAIN, EPI_RESID_F32>;
+  if (pro == PRO_F32 && epi == EPI_BIAS_F32) return gemv_batch_kernel<RPW, 1, PRO_F32, EPI_BIAS_F32>;
+  if (pro == PRO_F32 && epi == EPI_ACT_TABLE) return gemv_batch_kernel<RPW, 1, PRO_F32, EPI_ACT_TABLE>;
   return nullptr;
 }
 KernelFn pick(int rpw, int nseg, int pro, int epi) {
@@ -355,7 +418,7 @@ int gemv_batch_setup_attributes() {
     const int rpws[3] = {1, 2, 4};
     for (int rpw : rpws)
       for (int nseg = 1; nseg <= 2; ++nseg)
-        for (int pro = 0; pro < 2; ++pro)
+        for (int pro = 0; pro < kGemvProCount; ++pro)
           for (int epi = 0; epi < kGemvEpiCount; ++epi) {
             KernelFn f = pick(rpw, nseg, pro, epi);
             if (!f) continue;
@@ -387,6 +450,8 @@ int gemv_batch_launch(const GemvPlan& plan, cudaStream_t stream, bool pdl) {
     p.y += (size_t)b0 * p.y_stride;
     if (p.residual) p.residual += (size_t)b0 * p.y_stride;
     if (p.yf) p.yf += (size_t)b0 * p.y_stride;
+    if (p.xf) p.xf += (size_t)b0 * p.x_stride;
+    if (p.tok) p.tok += b0;
     if (b0 + per < plan.batch) p.pos_inc = nullptr;       // the position advances once, after the last launch
     B200_CUDA(launch_pdl(f, dim3(plan.grid), dim3(kThreads), (size_t)plan.smem, stream, pdl, p, plan.tmap));
   }

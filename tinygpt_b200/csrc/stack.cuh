@@ -78,8 +78,10 @@ struct StackAttn {
   void* out = nullptr;          // [n_tok, ld_out] T, head h at columns h·vdim
   int64_t ld_out = 0;
   // split keys (decode steps over long key lists): nsplit CTAs per (token, head), each over keys_per_split entries of
-  // the visible list, partial softmaxes [n_tok·heads][nsplit][2 + vdim] in split_ws, merged by a second launch
+  // the visible list, partial softmaxes [n_tok·heads][nsplit][2 + vdim] in split_ws; the CTA that finishes a pair last
+  // (split_tickets [n_tok·heads], zero-initialised, self-resetting) merges them
   float* split_ws = nullptr;
+  unsigned int* split_tickets = nullptr;
   int nsplit = 1, keys_per_split = 0;
 };
 constexpr int kStackSplitRows = 16;    // most rows a split-key attention launch serves

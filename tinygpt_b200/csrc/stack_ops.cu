@@ -195,6 +195,38 @@ __global__ void __launch_bounds__(128) stack_kv_store_kernel(const StackAttn p) 
   for (int i = threadIdx.x; i < nv; i += blockDim.x) vd[i] = row[p.off_v + i];
 }
 
+// One warp merges the key splits' partial softmaxes {max, sum, weighted values} of a (token, head) pair, applies the
+// gate and stores the head's output.  Run by the CTA that finishes a pair last (ticket), so it reads through L2.
+template <typename T>
+__device__ __forceinline__ void stack_attn_merge_pair(const StackAttn& p, int64_t pair, int t, int h, int lane) {
+  const int vdim = p.a.vdim;
+  const float* base = p.split_ws + (size_t)pair * p.nsplit * (2 + vdim);
+  // lanes over splits (nsplit <= 64: two per lane) for the maxima and the sums …
+  const int s0 = lane, s1 = lane + 32;
+  const float m0 = s0 < p.nsplit ? __ldcg(base + (size_t)s0 * (2 + vdim)) : -INFINITY;
+  const float m1 = s1 < p.nsplit ? __ldcg(base + (size_t)s1 * (2 + vdim)) : -INFINITY;
+  const float l0 = s0 < p.nsplit ? __ldcg(base + (size_t)s0 * (2 + vdim) + 1) : 0.f;
+  const float l1 = s1 < p.nsplit ? __ldcg(base + (size_t)s1 * (2 + vdim) + 1) : 0.f;
+  const float mt = warp_max(fmaxf(m0, m1));
+  const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - mt), f1 = m1 == -INFINITY ? 0.f : expf(m1 - mt);
+  const float l = warp_sum(l0 * f0 + l1 * f1);
+  const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  float gate = 1.f;
+  if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
+  const float fin = gate / l;
+  T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
+  // … then lanes over value columns, the splits' weights handed round by shuffle (independent loads per split)
+  for (int d0 = 0; d0 < vdim; d0 += 32) {
+    const int d = d0 + lane;
+    float a = 0.f;
+    for (int s = 0; s < p.nsplit; ++s) {
+      const float f = __shfl_sync(0xffffffffu, s < 32 ? f0 : f1, s & 31);
+      if (d < vdim && f != 0.f) a = fmaf(__ldcg(base + (size_t)s * (2 + vdim) + 2 + d), f, a);
+    }
+    if (d < vdim) orow[d] = cvt<T>(a * fin);
+  }
+}
+
 // NW warps per (token, query head); NW = 1: four pairs per CTA (prompts: pairs abound), NW = 4: one pair per CTA, its keys
 // dealt to the warps 32 at a time and the partial softmaxes merged through shared memory (decode steps: few pairs, long
 // key lists).  The visible keys of a query at position i are the kept first rows [0, min(keep_first, lo)) followed by
@@ -338,6 +370,16 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
         o[1] = l;
       }
       cols([&](int d, float& a) { o[2 + d] = a; });
+      // the CTA that hands in a pair's last partial merges them (tickets start at zero and reset themselves)
+      __threadfence();
+      __syncwarp();
+      unsigned int tk = 0;
+      if (lane == 0) tk = atomicAdd(p.split_tickets + pair, 1u);
+      tk = __shfl_sync(0xffffffffu, tk, 0);
+      if (tk != (unsigned int)p.nsplit - 1u) return;
+      if (lane == 0) p.split_tickets[pair] = 0;
+      __threadfence();
+      stack_attn_merge_pair<T>(p, pair, t, h, lane);
       return;
     }
   }
@@ -346,41 +388,6 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
   const float fin = gate / l;
   cols([&](int d, float& a) { orow[d] = cvt<T>(a * fin); });
-}
-
-// one warp per (token, head): merge the splits' partial softmaxes, apply the gate, store
-template <typename T>
-__global__ void __launch_bounds__(128) stack_attn_merge_kernel(const StackAttn p) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t pair = (int64_t)blockIdx.x * 4 + warp;
-  const int t = (int)(pair / p.a.heads), h = (int)(pair % p.a.heads);
-  if (t >= p.n_tok) return;
-  const int vdim = p.a.vdim;
-  const float* base = p.split_ws + (size_t)pair * p.nsplit * (2 + vdim);
-  // lanes over splits (nsplit <= 64: two per lane) for the maxima and the sums …
-  const int s0 = lane, s1 = lane + 32;
-  const float m0 = s0 < p.nsplit ? base[(size_t)s0 * (2 + vdim)] : -INFINITY;
-  const float m1 = s1 < p.nsplit ? base[(size_t)s1 * (2 + vdim)] : -INFINITY;
-  const float l0 = s0 < p.nsplit ? base[(size_t)s0 * (2 + vdim) + 1] : 0.f;
-  const float l1 = s1 < p.nsplit ? base[(size_t)s1 * (2 + vdim) + 1] : 0.f;
-  const float mt = warp_max(fmaxf(m0, m1));
-  const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - mt), f1 = m1 == -INFINITY ? 0.f : expf(m1 - mt);
-  const float l = warp_sum(l0 * f0 + l1 * f1);
-  const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
-  float gate = 1.f;
-  if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
-  const float fin = gate / l;
-  T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
-  // … then lanes over value columns, the splits' weights handed round by shuffle (independent loads per split)
-  for (int d0 = 0; d0 < vdim; d0 += 32) {
-    const int d = d0 + lane;
-    float a = 0.f;
-    for (int s = 0; s < p.nsplit; ++s) {
-      const float f = __shfl_sync(0xffffffffu, s < 32 ? f0 : f1, s & 31);
-      if (d < vdim && f != 0.f) a = fmaf(base[(size_t)s * (2 + vdim) + 2 + d], f, a);
-    }
-    if (d < vdim) orow[d] = cvt<T>(a * fin);
-  }
 }
 
 __global__ void __launch_bounds__(256) stack_bias_add_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ b,
@@ -558,7 +565,8 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
   int rc = check_attn(p);
   if (rc != B200_OK) return rc;
   B200_CHECK_ARG(p.out != nullptr, "stack attention: null output");
-  B200_CHECK_ARG(p.split_ws == nullptr || (p.nsplit >= 1 && p.keys_per_split > 0 && p.n_tok <= kStackSplitRows),
+  B200_CHECK_ARG(p.split_ws == nullptr || (p.split_tickets != nullptr && p.nsplit >= 1 && p.nsplit <= kStackMaxSplits &&
+                                           p.keys_per_split > 0 && p.n_tok <= kStackSplitRows),
                  "stack attention: bad key split");
   // few (token, head) pairs: four warps share one pair's keys
   const bool wide = p.split_ws != nullptr || (int64_t)p.n_tok * p.a.heads < 4 * 148 * 4;
@@ -576,11 +584,7 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
     if (wide) B200_CUDA((launch_attn_t<__nv_bfloat16, 4, false>(p, st)));
     else B200_CUDA((launch_attn_t<__nv_bfloat16, 1, false>(p, st)));
   }
-  if (p.split_ws != nullptr) {
-    const dim3 grid((unsigned)(((int64_t)p.n_tok * p.a.heads + 3) / 4));
-    if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_attn_merge_kernel<float>, grid, dim3(128), 0, st, false, p));
-    else B200_CUDA(launch_pdl(stack_attn_merge_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, false, p));
-  }
+
   return B200_OK;
 }
 
