@@ -282,7 +282,7 @@ static int stack_product_head(StackEngine* s, const float* x, const int32_t* row
     pl.p.y = s->logits_bf;
     pl.p.yf = s->logits;
     if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
-    return gemv_launch(pl, st, s->pdl);
+    return gemv_launch(pl, st, false);   // copies and the argmax follow: a full dependency
   }
   if ((rc = launch_stack_rmsnorm(s->hn, x, d.final_norm, rows, n_rows, d.width, d.norm_eps, d.norm_offset, s->dtype, st)) !=
       B200_OK)
@@ -293,7 +293,7 @@ static int stack_product_head(StackEngine* s, const float* x, const int32_t* row
     pl.p.y = s->logits_bf;
     pl.p.yf = s->logits;
     if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
-    return gemv_launch(pl, st, s->pdl);
+    return gemv_launch(pl, st, false);   // copies and the argmax follow: a full dependency
   }
   StackGemm g;
   g.a = s->hn; g.lda = d.width; g.k1 = d.width;

@@ -14,6 +14,8 @@ enum StackEpi : int {
   SEPI_LOGITS = 4,    // C_f32[m, n] = acc and C2_bf16[m, n] = bf16(acc)    (fp32 logits + the sampler's bf16 copy)
 };
 
+bool stack_pdl();   // kernels of stack_ops.cu are launched under programmatic dependent launch unless B200_NO_PDL=1
+
 struct StackGemm {
   // A is [M, K]: columns [0, k1) come from a, the rest from a2 (the [x; x0] concatenation without a copy).  a_f32: the
   // source is the fp32 residual stream, rounded to T when it is loaded (a bf16 product takes bf16 operands).

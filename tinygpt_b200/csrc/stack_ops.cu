@@ -5,6 +5,15 @@
 #include "stack.cuh"
 
 namespace b200 {
+
+// Every kernel of this file starts with griddepcontrol.launch_dependents + griddepcontrol.wait, so it may be launched
+// ahead of the end of its predecessor (programmatic dependent launch): the launch latency hides behind the predecessor's
+// tail and nothing is read or written before the predecessor's results are complete.  B200_NO_PDL=1 turns it off.
+bool stack_pdl() {
+  static const bool on = !env_flag("B200_NO_PDL", false);
+  return on;
+}
+
 namespace {
 
 template <typename T> __device__ __forceinline__ float ldf(const T* p);
@@ -42,6 +51,8 @@ constexpr int kBM = 64, kBN = 64, kBK = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(256) stack_gemm_kernel(const StackGemm g) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float As[kBK][kBM + 4];
   __shared__ float Ws[kBK][kBN + 4];
   const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
@@ -115,6 +126,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) stack_rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ x,
                                                             const float* __restrict__ w, const int32_t* __restrict__ rows,
                                                             int dim, float eps, float offset) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[8];
   const int64_t src = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
   const float* xr = x + src * dim;
@@ -128,6 +141,8 @@ __global__ void __launch_bounds__(256) stack_rmsnorm_kernel(T* __restrict__ y, c
 template <typename YT>
 __global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ x, const YT* __restrict__ y,
                                                             const float* __restrict__ w, int dim, float eps, float mult) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float red[8];
   const YT* yr = y + (int64_t)blockIdx.x * dim;
   float* xr = x + (int64_t)blockIdx.x * dim;
@@ -139,6 +154,8 @@ __global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ 
 
 __global__ void __launch_bounds__(256) stack_cast_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ x,
                                                          int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
     y[e] = __float2bfloat16_rn(x[e]);
 }
@@ -148,6 +165,8 @@ __global__ void __launch_bounds__(256) stack_act_table_kernel(__nv_bfloat16* __r
                                                               const __nv_bfloat16* __restrict__ table,
                                                               const int32_t* __restrict__ tok, int64_t table_ld, int col,
                                                               int n, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = e / n;
     const int j = (int)(e % n);
@@ -159,6 +178,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) stack_act_mul_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ g,
                                                             const T* __restrict__ u, int64_t ld_gu, int n, int act,
                                                             int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = e / n;
     const int j = (int)(e % n);
@@ -173,6 +194,8 @@ template <typename T>
 __global__ void __launch_bounds__(128) stack_embed_kernel(float* __restrict__ x, float* __restrict__ x0,
                                                           const T* __restrict__ embed, const int32_t* __restrict__ tok,
                                                           int vocab, int width, float scale) {
+  pdl_trigger();
+  pdl_wait();
   int id = tok[blockIdx.x];
   if (id < 0 || id >= vocab) id = 0;
   const T* row = embed + (int64_t)id * width;
@@ -186,6 +209,8 @@ __global__ void __launch_bounds__(128) stack_embed_kernel(float* __restrict__ x,
 // ----------------------------------------------------------------------------------------------------------- attention
 template <typename T>
 __global__ void __launch_bounds__(128) stack_kv_store_kernel(const StackAttn p) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int nk = p.a.kv_heads * p.a.dim, nv = p.a.kv_heads * p.a.vdim;
   const T* row = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
@@ -237,6 +262,8 @@ __device__ __forceinline__ void stack_attn_merge_pair(const StackAttn& p, int64_
 // per pass (the groups' sums meet in a butterfly after the walk).
 template <typename T, int VR, int NW, bool VEC>
 __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float smem_f[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int wi = warp % NW;
@@ -392,17 +419,23 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
 
 __global__ void __launch_bounds__(256) stack_bias_add_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ b,
                                                              int n, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
     y[e] = __float2bfloat16_rn(__bfloat162float(y[e]) + b[e % n]);
 }
 __global__ void __launch_bounds__(256) stack_axpy_kernel(float* __restrict__ x, const __nv_bfloat16* __restrict__ t,
                                                          float mult, int add, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x)
     x[e] = (add ? x[e] : 0.f) + mult * __bfloat162float(t[e]);
 }
 __global__ void __launch_bounds__(256) stack_cat_cast_kernel(__nv_bfloat16* __restrict__ cat, const float* __restrict__ a,
                                                              const float* __restrict__ b, float* __restrict__ zero,
                                                              int width, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = e / width;
     const int j = (int)(e % width);
@@ -429,8 +462,8 @@ int launch_stack_gemm(const StackGemm& g, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(g.k1 == g.K || g.a2 != nullptr, "stack gemm: second operand source missing");
   B200_CHECK_ARG(g.epi != SEPI_ACT_TABLE || (g.table && g.tok), "stack gemm: table epilogue without a table");
   const dim3 grid((g.N + kBN - 1) / kBN, (g.M + kBM - 1) / kBM);
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_gemm_kernel<float>, grid, dim3(256), 0, st, false, g));
-  else B200_CUDA(launch_pdl(stack_gemm_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, false, g));
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_gemm_kernel<float>, grid, dim3(256), 0, st, stack_pdl(), g));
+  else B200_CUDA(launch_pdl(stack_gemm_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, stack_pdl(), g));
   return B200_OK;
 }
 
@@ -439,10 +472,10 @@ int launch_stack_rmsnorm(void* y, const float* x, const float* w, const int32_t*
   STACK_DTYPE_CHECK(dtype);
   B200_CHECK_ARG(y && x && w && n_rows > 0 && dim > 0, "stack rmsnorm: bad arguments");
   if (dtype == B200_F32)
-    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<float>, dim3((unsigned)n_rows), dim3(256), 0, st, false, (float*)y, x, w, rows,
+    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<float>, dim3((unsigned)n_rows), dim3(256), 0, st, stack_pdl(), (float*)y, x, w, rows,
                          dim, eps, offset));
   else
-    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(256), 0, st, false,
+    B200_CUDA(launch_pdl(stack_rmsnorm_kernel<__nv_bfloat16>, dim3((unsigned)n_rows), dim3(256), 0, st, stack_pdl(),
                          (__nv_bfloat16*)y, x, w, rows, dim, eps, offset));
   return B200_OK;
 }
@@ -450,21 +483,21 @@ int launch_stack_rmsnorm(void* y, const float* x, const float* w, const int32_t*
 int launch_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int dim, float eps, float mult,
                          cudaStream_t st) {
   B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
-  B200_CUDA(launch_pdl(stack_rms_add_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps, mult));
+  B200_CUDA(launch_pdl(stack_rms_add_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x, y, w, dim, eps, mult));
   return B200_OK;
 }
 
 int launch_stack_rms_add_bf16(float* x, const __nv_bfloat16* y, const float* w, int64_t rows, int dim, float eps, float mult,
                               cudaStream_t st) {
   B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
-  B200_CUDA(launch_pdl(stack_rms_add_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, st, false, x, y, w, dim, eps,
+  B200_CUDA(launch_pdl(stack_rms_add_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x, y, w, dim, eps,
                        mult));
   return B200_OK;
 }
 
 int launch_stack_cast(__nv_bfloat16* y, const float* x, int64_t total, cudaStream_t st) {
   B200_CHECK_ARG(y && x && total > 0, "stack cast: bad arguments");
-  B200_CUDA(launch_pdl(stack_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, x, total));
+  B200_CUDA(launch_pdl(stack_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), y, x, total));
   return B200_OK;
 }
 
@@ -472,7 +505,7 @@ int launch_stack_act_table(__nv_bfloat16* y, const __nv_bfloat16* g, const void*
                            int col, int64_t rows, int n, cudaStream_t st) {
   B200_CHECK_ARG(y && g && table && tok && rows > 0 && n > 0, "stack act_table: bad arguments");
   const int64_t total = rows * n;
-  B200_CUDA(launch_pdl(stack_act_table_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, g,
+  B200_CUDA(launch_pdl(stack_act_table_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), y, g,
                        (const __nv_bfloat16*)table, tok, table_ld, col, n, total));
   return B200_OK;
 }
@@ -484,10 +517,10 @@ int launch_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, in
   B200_CHECK_ARG(act == B200_ACT_GELU_TANH || act == B200_ACT_SILU, "stack act_mul: unknown activation %d", act);
   const int64_t total = rows * n;
   if (dtype == B200_F32)
-    B200_CUDA(launch_pdl(stack_act_mul_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, (float*)y, ld_y,
+    B200_CUDA(launch_pdl(stack_act_mul_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), (float*)y, ld_y,
                          (const float*)g, (const float*)u, ld_gu, n, act, total));
   else
-    B200_CUDA(launch_pdl(stack_act_mul_kernel<__nv_bfloat16>, dim3(grid_cap(total, 256)), dim3(256), 0, st, false,
+    B200_CUDA(launch_pdl(stack_act_mul_kernel<__nv_bfloat16>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(),
                          (__nv_bfloat16*)y, ld_y, (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, ld_gu, n, act, total));
   return B200_OK;
 }
@@ -497,10 +530,10 @@ int launch_stack_embed(float* x, float* x0, const void* embed, const int32_t* to
   STACK_DTYPE_CHECK(dtype);
   B200_CHECK_ARG(x && x0 && embed && tok && n_tok > 0, "stack embed: bad arguments");
   if (dtype == B200_F32)
-    B200_CUDA(launch_pdl(stack_embed_kernel<float>, dim3((unsigned)n_tok), dim3(128), 0, st, false, x, x0,
+    B200_CUDA(launch_pdl(stack_embed_kernel<float>, dim3((unsigned)n_tok), dim3(128), 0, st, stack_pdl(), x, x0,
                          (const float*)embed, tok, vocab, width, scale));
   else
-    B200_CUDA(launch_pdl(stack_embed_kernel<__nv_bfloat16>, dim3((unsigned)n_tok), dim3(128), 0, st, false, x, x0,
+    B200_CUDA(launch_pdl(stack_embed_kernel<__nv_bfloat16>, dim3((unsigned)n_tok), dim3(128), 0, st, stack_pdl(), x, x0,
                          (const __nv_bfloat16*)embed, tok, vocab, width, scale));
   return B200_OK;
 }
@@ -508,13 +541,13 @@ int launch_stack_embed(float* x, float* x0, const void* embed, const int32_t* to
 int launch_stack_bias_add(__nv_bfloat16* y, const float* b, int64_t rows, int n, cudaStream_t st) {
   B200_CHECK_ARG(y && b && rows > 0 && n > 0, "stack bias_add: bad arguments");
   const int64_t total = rows * n;
-  B200_CUDA(launch_pdl(stack_bias_add_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, y, b, n, total));
+  B200_CUDA(launch_pdl(stack_bias_add_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), y, b, n, total));
   return B200_OK;
 }
 
 int launch_stack_axpy(float* x, const __nv_bfloat16* t, float mult, bool add, int64_t total, cudaStream_t st) {
   B200_CHECK_ARG(x && t && total > 0, "stack axpy: bad arguments");
-  B200_CUDA(launch_pdl(stack_axpy_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, x, t, mult, add ? 1 : 0, total));
+  B200_CUDA(launch_pdl(stack_axpy_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), x, t, mult, add ? 1 : 0, total));
   return B200_OK;
 }
 
@@ -522,7 +555,7 @@ int launch_stack_cat_cast(__nv_bfloat16* cat, const float* a, const float* b, fl
                           cudaStream_t st) {
   B200_CHECK_ARG(cat && a && b && rows > 0 && width > 0, "stack cat_cast: bad arguments");
   const int64_t total = rows * width;
-  B200_CUDA(launch_pdl(stack_cat_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, cat, a, b, zero, width,
+  B200_CUDA(launch_pdl(stack_cat_cast_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), cat, a, b, zero, width,
                        total));
   return B200_OK;
 }
@@ -542,8 +575,8 @@ int launch_stack_kv_store(const StackAttn& p, int dtype, cudaStream_t st) {
   STACK_DTYPE_CHECK(dtype);
   int rc = check_attn(p);
   if (rc != B200_OK) return rc;
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_kv_store_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, false, p));
-  else B200_CUDA(launch_pdl(stack_kv_store_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, false, p));
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_kv_store_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(stack_kv_store_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   return B200_OK;
 }
 
@@ -554,10 +587,10 @@ static cudaError_t launch_attn_t(const StackAttn& p, cudaStream_t st) {
   const dim3 grid((unsigned)((pairs + ppb - 1) / ppb), (unsigned)((NW > 1 && p.split_ws != nullptr) ? p.nsplit : 1));
   const size_t smem = ((size_t)4 * p.a.dim + (NW > 1 ? (size_t)NW * (2 + p.a.vdim) : 0)) * sizeof(float);
   const int vr = (p.a.vdim + 31) / 32;
-  if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1, NW, VEC>, grid, dim3(128), smem, st, false, p);
-  if (vr <= 2) return launch_pdl(stack_attn_kernel<T, 2, NW, VEC>, grid, dim3(128), smem, st, false, p);
-  if (vr <= 4) return launch_pdl(stack_attn_kernel<T, 4, NW, VEC>, grid, dim3(128), smem, st, false, p);
-  return launch_pdl(stack_attn_kernel<T, 8, NW, VEC>, grid, dim3(128), smem, st, false, p);
+  if (vr <= 1) return launch_pdl(stack_attn_kernel<T, 1, NW, VEC>, grid, dim3(128), smem, st, stack_pdl(), p);
+  if (vr <= 2) return launch_pdl(stack_attn_kernel<T, 2, NW, VEC>, grid, dim3(128), smem, st, stack_pdl(), p);
+  if (vr <= 4) return launch_pdl(stack_attn_kernel<T, 4, NW, VEC>, grid, dim3(128), smem, st, stack_pdl(), p);
+  return launch_pdl(stack_attn_kernel<T, 8, NW, VEC>, grid, dim3(128), smem, st, stack_pdl(), p);
 }
 
 int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
