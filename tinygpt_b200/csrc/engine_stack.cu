@@ -428,7 +428,11 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bo
     const int hv = L.attn.heads * L.attn.vdim;
     if (hv != L.off_act || L.off_act + L.ff != L.k_out)   // padding columns meet zero weights: keep them finite
       B200_CUDA(cudaMemsetAsync(s->mid, 0, (size_t)n_tok * L.k_out * s->esz, st));
-    if ((rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
+    // steps in which every row is its sequence's only new row (decode) append K/V inside the attention launch
+    bool single = true;
+    for (const StackEngine::Seg& g : s->segs) single = single && g.count == 1;
+    a.own_from_proj = single ? 1 : 0;
+    if (!a.own_from_proj && (rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
     if ((rc = stack_attention(s, a, L, st)) != B200_OK) return rc;
     if (L.ff > 0) {
       const uint8_t* p = (const uint8_t*)s->proj;

@@ -84,6 +84,9 @@ struct StackAttn {
   // (split_tickets [n_tok·heads], zero-initialised, self-resetting) merges them
   float* split_ws = nullptr;
   unsigned int* split_tickets = nullptr;
+  // decode steps (every row the only new row of its sequence): the row's own key / value are read from proj and one
+  // CTA per (row, kv head) appends them to the cache in the same launch — no separate kv_store
+  int own_from_proj = 0;
   int nsplit = 1, keys_per_split = 0;
 };
 constexpr int kStackSplitRows = 16;    // most rows a split-key attention launch serves

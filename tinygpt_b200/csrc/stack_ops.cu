@@ -285,6 +285,15 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   const int total = na + (i - lo + 1);
   // this CTA's share of the visible list (all of it unless the keys are split over blockIdx.y)
   const bool split = NW > 1 && p.split_ws != nullptr;
+  // the row's own key / value: from proj when the launch also appends them (own_from_proj), else already in the cache
+  const T* own_k = prow + p.off_k + kvh * dim;
+  const T* own_v = prow + p.off_v + kvh * vdim;
+  if (p.own_from_proj && wi == 0 && blockIdx.y == 0 && h % (p.a.heads / p.a.kv_heads) == 0) {
+    T* kd = static_cast<T*>(p.kcache) + (int64_t)slot * p.k_slot_stride + (int64_t)i * krs + kvh * dim;
+    T* vd = static_cast<T*>(p.vcache) + (int64_t)slot * p.v_slot_stride + (int64_t)i * vrs + kvh * vdim;
+    for (int d = lane; d < dim; d += 32) kd[d] = own_k[d];
+    for (int d = lane; d < vdim; d += 32) vd[d] = own_v[d];
+  }
   const int begin = split ? (int)blockIdx.y * p.keys_per_split : 0;
   const int end = split ? min(total, begin + p.keys_per_split) : total;
   constexpr int NA = VEC ? 8 : VR;
@@ -312,15 +321,26 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     const int j = idx < na ? idx : lo + (idx - na);
     float s = -INFINITY;
     if (valid) {
-      const T* kr = kb + (int64_t)j * krs;
+      const T* kr = (p.own_from_proj && j == i) ? own_k : kb + (int64_t)j * krs;
       float dot = 0.f;
       if constexpr (VEC) {
+        // eight 16-byte pieces of the key row are requested together, then consumed: the row costs dim/64 memory
+        // round trips instead of dim/8
         const uint4* k4 = reinterpret_cast<const uint4*>(kr);
-        for (int d8 = 0; d8 < (dim >> 3); ++d8) {
-          float kf[8];
-          unpack8(k4[d8], kf);
+        const int nd8 = dim >> 3;
+        for (int d0 = 0; d0 < nd8; d0 += 8) {
+          uint4 kq[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) dot = fmaf(qs[d8 * 8 + e], kf[e], dot);
+          for (int u = 0; u < 8; ++u) kq[u] = d0 + u < nd8 ? k4[d0 + u] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (d0 + u < nd8) {
+              float kf[8];
+              unpack8(kq[u], kf);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) dot = fmaf(qs[(d0 + u) * 8 + e], kf[e], dot);
+            }
+          }
         }
       } else {
         for (int d = 0; d < dim; ++d) dot = fmaf(qs[d], ldf<T>(kr + d), dot);
@@ -337,22 +357,36 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     if constexpr (VEC) {
       const int G = vdim >> 3, KP = 32 / G;   // lanes per value row, rows per pass
       const int grp = lane / G, gl = lane % G;
-      for (int jj = 0; jj < cn; jj += KP) {
-        const int src = jj + grp;             // < 32: jj is a multiple of KP and grp < KP
-        const float pw = __shfl_sync(0xffffffffu, pj, src);
-        const int jr = __shfl_sync(0xffffffffu, j, src);
-        if (src < cn) {
-          float vf[8];
-          unpack8(*reinterpret_cast<const uint4*>(vb + (int64_t)jr * vrs + gl * 8), vf);
+      // eight passes' value pieces are requested together, then consumed (as for the key rows)
+      for (int jj0 = 0; jj0 < cn; jj0 += 8 * KP) {
+        uint4 vq[8];
+        float pw[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(pw, vf[e], acc[e]);
+        for (int u = 0; u < 8; ++u) {
+          const int src = jj0 + u * KP + grp;   // key of this lane's row group in pass u
+          pw[u] = __shfl_sync(0xffffffffu, pj, src & 31);
+          const int jr = __shfl_sync(0xffffffffu, j, src & 31);
+          vq[u] = make_uint4(0, 0, 0, 0);
+          if (src < cn) {
+            const T* vr = (p.own_from_proj && jr == i) ? own_v : vb + (int64_t)jr * vrs;
+            vq[u] = *reinterpret_cast<const uint4*>(vr + gl * 8);
+          } else {
+            pw[u] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          float vf[8];
+          unpack8(vq[u], vf);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(pw[u], vf[e], acc[e]);
         }
       }
     } else {
       for (int jj = 0; jj < cn; ++jj) {
         const float pw = __shfl_sync(0xffffffffu, pj, jj);
         const int jr = __shfl_sync(0xffffffffu, j, jj);
-        const T* vr = vb + (int64_t)jr * vrs;
+        const T* vr = (p.own_from_proj && jr == i) ? own_v : vb + (int64_t)jr * vrs;
 #pragma unroll
         for (int r = 0; r < VR; ++r) {
           const int d = lane + 32 * r;
@@ -606,6 +640,8 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
   const int vd = p.a.vdim;
   const bool vec = dtype == B200_BF16 && p.a.dim % 8 == 0 && vd >= 8 && vd <= 256 && (vd & (vd - 1)) == 0 &&
                    p.k_slot_stride % 8 == 0 && p.v_slot_stride % 8 == 0 &&
+                   (!p.own_from_proj || (p.off_k % 8 == 0 && p.off_v % 8 == 0 && p.ld_proj % 8 == 0 &&
+                                         (reinterpret_cast<uintptr_t>(p.proj) & 15) == 0)) &&
                    ((reinterpret_cast<uintptr_t>(p.kcache) | reinterpret_cast<uintptr_t>(p.vcache)) & 15) == 0;
   if (dtype == B200_F32) {
     if (wide) B200_CUDA((launch_attn_t<float, 4, false>(p, st)));
