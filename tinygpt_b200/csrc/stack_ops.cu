@@ -146,6 +146,28 @@ __global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ 
   __shared__ float red[8];
   const YT* yr = y + (int64_t)blockIdx.x * dim;
   float* xr = x + (int64_t)blockIdx.x * dim;
+  if (dim <= 16 * (int)blockDim.x && gridDim.x <= 64) {
+    // few rows (decode steps: latency counts) and the row fits the CTA's registers: y, w and x are requested
+    // together, one memory round trip before the reduction
+    float yv[16], wv[16], xv[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      yv[k] = i < dim ? ldf<YT>(yr + i) : 0.f;
+      wv[k] = i < dim ? w[i] : 0.f;
+      xv[k] = i < dim ? xr[i] : 0.f;
+    }
+    float s2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) s2 += yv[k] * yv[k];
+    const float inv2 = 1.f / sqrtf(block_sum(s2, red) / (float)dim + eps);
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < dim) xr[i] = xv[k] + mult * (yv[k] * inv2 * wv[k]);
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += ldf<YT>(yr + i) * ldf<YT>(yr + i);
   const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
@@ -246,7 +268,8 @@ __device__ __forceinline__ void stack_attn_merge_pair(const StackAttn& p, int64_
     float a = 0.f;
     for (int s = 0; s < p.nsplit; ++s) {
       const float f = __shfl_sync(0xffffffffu, s < 32 ? f0 : f1, s & 31);
-      if (d < vdim && f != 0.f) a = fmaf(__ldcg(base + (size_t)s * (2 + vdim) + 2 + d), f, a);
+      // (an empty split holds zeros: no guard, so the loads do not wait for the weights)
+      if (d < vdim) a = fmaf(__ldcg(base + (size_t)s * (2 + vdim) + 2 + d), f, a);
     }
     if (d < vdim) orow[d] = cvt<T>(a * fin);
   }

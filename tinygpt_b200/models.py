@@ -356,7 +356,7 @@ def kozusun_tensor_shapes(spec: StackSpec) -> Dict[str, Tuple[int, ...]]:
 
 
 def synth_kozusun_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> Dict[str, torch.Tensor]:
-    """Seeded synthetic Kozusun checkpoint (bf16, checkpoint names): matrices N(0, std·√(256/in)), vectors N(0, 0.1)."""
+    """Seeded synthetic Kozusun checkpoint (bf16, checkpoint names): matrices N(0, std·√(64/in)), vectors N(0, 0.1)."""
     g = torch.Generator().manual_seed(seed)
     w = {}
     for name, shape in kozusun_tensor_shapes(spec).items():
@@ -365,7 +365,7 @@ def synth_kozusun_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> 
             if name.endswith("side.norm"):
                 t = t + 1.0
         else:
-            t = torch.randn(shape, generator=g) * (std * (256.0 / shape[1]) ** 0.5)
+            t = torch.randn(shape, generator=g) * (std * (64.0 / shape[1]) ** 0.5)
         w[name] = t.to(torch.bfloat16)
     return w
 
