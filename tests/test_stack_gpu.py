@@ -323,6 +323,27 @@ def test_long_prompts_big_heads_and_split_keys(dtype, hd):
     eng.close()
 
 
+def test_fast_products_agree_with_the_general_kernels(monkeypatch):
+    """bf16: the GEMV / tcgen05 / tensor-core-attention routes against the same engine held on the general kernels
+    (B200_STACK_PLAIN=1) — same rounding points up to summation order, so far tighter than against the fp32 restatement."""
+    cfg = so.make_config(width=128, vocab=160, side_dim=64, loop=(0, 1, 2),
+                         layers=[dict(heads=4, kv_heads=2, dim=64, vdim=64, size=40, keep_first=3, ff=96),
+                                 dict(heads=2, kv_heads=1, dim=128, vdim=128, size=200, keep_first=0, ff=64)])
+    w = so.make_weights(cfg, seed=21)
+    toks = tokens(150, cfg["vocab"], 22)
+
+    def run():
+        eng = make_engine(cfg, w, torch.bfloat16, max_ctx=300)
+        out = [eng.step([(0, toks[:140], list(range(140)))])] + [eng.step([(0, [t], [0])]) for t in toks[140:]]
+        eng.close()
+        return torch.cat(out)
+
+    fast = run()
+    monkeypatch.setenv("B200_STACK_PLAIN", "1")
+    plain = run()
+    assert rel_err(fast, plain) < 3e-2
+
+
 def test_residual_stream_mechanisms_show_in_the_logits():
     """Each constant matters: dropping the kept tokens, shifting the window by one, dropping the side input or the loop's
     re-read of the embedding moves the oracle's logits by far more than the engine's distance to the true design."""

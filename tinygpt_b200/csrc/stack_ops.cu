@@ -146,32 +146,40 @@ __global__ void __launch_bounds__(256) stack_rms_add_kernel(float* __restrict__ 
   __shared__ float red[8];
   const YT* yr = y + (int64_t)blockIdx.x * dim;
   float* xr = x + (int64_t)blockIdx.x * dim;
-  if (dim <= 16 * (int)blockDim.x && gridDim.x <= 64) {
-    // few rows (decode steps: latency counts) and the row fits the CTA's registers: y, w and x are requested
-    // together, one memory round trip before the reduction
-    float yv[16], wv[16], xv[16];
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int i = threadIdx.x + k * blockDim.x;
-      yv[k] = i < dim ? ldf<YT>(yr + i) : 0.f;
-      wv[k] = i < dim ? w[i] : 0.f;
-      xv[k] = i < dim ? xr[i] : 0.f;
-    }
-    float s2 = 0.f;
-#pragma unroll
-    for (int k = 0; k < 16; ++k) s2 += yv[k] * yv[k];
-    const float inv2 = 1.f / sqrtf(block_sum(s2, red) / (float)dim + eps);
-#pragma unroll
-    for (int k = 0; k < 16; ++k) {
-      const int i = threadIdx.x + k * blockDim.x;
-      if (i < dim) xr[i] = xv[k] + mult * (yv[k] * inv2 * wv[k]);
-    }
-    return;
-  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) ss += ldf<YT>(yr + i) * ldf<YT>(yr + i);
   const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
   for (int i = threadIdx.x; i < dim; i += blockDim.x) xr[i] += mult * (ldf<YT>(yr + i) * inv * w[i]);
+}
+
+// The same for a few rows that fit the CTA's registers (decode steps, where latency counts): y, w and x are requested
+// together — one memory round trip before the reduction instead of three.  dim <= 16 · 256.
+template <typename YT>
+__global__ void __launch_bounds__(256) stack_rms_add_small_kernel(float* __restrict__ x, const YT* __restrict__ y,
+                                                                  const float* __restrict__ w, int dim, float eps,
+                                                                  float mult) {
+  __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
+  const YT* yr = y + (int64_t)blockIdx.x * dim;
+  float* xr = x + (int64_t)blockIdx.x * dim;
+  float yv[16], wv[16], xv[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const int i = threadIdx.x + k * 256;
+    yv[k] = i < dim ? ldf<YT>(yr + i) : 0.f;
+    wv[k] = i < dim ? w[i] : 0.f;
+    xv[k] = i < dim ? xr[i] : 0.f;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) ss += yv[k] * yv[k];
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < dim) xr[i] = xv[k] + mult * (yv[k] * inv * wv[k]);
+  }
 }
 
 __global__ void __launch_bounds__(256) stack_cast_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ x,
@@ -474,6 +482,155 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   cols([&](int d, float& a) { orow[d] = cvt<T>(a * fin); });
 }
 
+// Decode-shaped steps (every row its sequence's only new row) of bf16 engines with key size <= 128 and value size 64 or
+// 128: one CTA per (row, head, split of 128 visible keys), warp w takes keys 32w … of the split, ONE key per lane.
+// The cached rows a lane needs — its key's 16-byte pieces and its row group's value pieces — are requested BEFORE the
+// programmatic-dependency wait: they were written by earlier steps, and the row's slot and position by the step's
+// first kernel, so all of it is stable while the projection that produces q still runs.  After the wait: q, the row's
+// own key / value from proj (appended to the cache by one CTA per KV head), scores, one softmax per warp, values, the
+// four warps merged through shared memory, the splits by ticket (stack_attn_merge_pair).
+__global__ void __launch_bounds__(128) stack_attn_decode_kernel(const StackAttn p) {
+  using T = __nv_bfloat16;
+  extern __shared__ float smem_f[];
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t pair = blockIdx.x;
+  const int t = (int)(pair / p.a.heads), h = (int)(pair % p.a.heads);
+  const int dim = p.a.dim, vdim = p.a.vdim, nd8 = dim >> 3;
+  const int G = vdim >> 3, KP = 32 / G;       // lanes per value row, value rows per pass; G passes cover 32 keys
+  const int grp = lane / G, gl = lane % G;
+  const int slot = p.slot[t], i = p.pos[t];
+  const int kvh = h / (p.a.heads / p.a.kv_heads);
+  const int64_t krs = (int64_t)p.a.kv_heads * dim, vrs = (int64_t)p.a.kv_heads * vdim;
+  const T* kb = static_cast<const T*>(p.kcache) + (int64_t)slot * p.k_slot_stride + kvh * dim;
+  const T* vb = static_cast<const T*>(p.vcache) + (int64_t)slot * p.v_slot_stride + kvh * vdim;
+  const int lo = p.a.window > 0 ? max(0, i - p.a.window + 1) : 0;
+  const int na = min(p.a.keep_first, lo);
+  const int total = na + (i - lo + 1);
+  const int begin = (int)blockIdx.y * p.keys_per_split;
+  const int end = min(total, begin + p.keys_per_split);
+  const int c0 = begin + warp * 32;            // keys_per_split <= 128: one chunk per warp
+  const int idx = c0 + lane;
+  const bool valid = idx < end;
+  const int j = idx < na ? idx : lo + (idx - na);
+  const int cn = max(0, min(32, end - c0));
+  // ---- cached rows, ahead of the wait
+  uint4 kq[16], vq[16];
+  int vj[16];
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    kq[u] = make_uint4(0, 0, 0, 0);
+    if (valid && j != i && u < nd8) kq[u] = reinterpret_cast<const uint4*>(kb + (int64_t)j * krs)[u];
+  }
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    const int src = u * KP + grp;              // key (within the chunk) of this lane's row group in pass u
+    vj[u] = __shfl_sync(0xffffffffu, j, src & 31);
+    vq[u] = make_uint4(0, 0, 0, 0);
+    if (u < G && src < cn && vj[u] != i) vq[u] = *reinterpret_cast<const uint4*>(vb + (int64_t)vj[u] * vrs + gl * 8);
+  }
+  pdl_wait();
+  // ---- what this step produced: q, the gate logit, the row's own key and value
+  float* qs = smem_f;                          // [dim], shared by the four warps
+  const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  for (int d = threadIdx.x; d < dim; d += 128) qs[d] = __bfloat162float(prow[p.off_q + h * dim + d]);
+  const T* own_k = prow + p.off_k + kvh * dim;
+  const T* own_v = prow + p.off_v + kvh * vdim;
+  if (valid && j == i) {
+#pragma unroll
+    for (int u = 0; u < 16; ++u)
+      if (u < nd8) kq[u] = reinterpret_cast<const uint4*>(own_k)[u];
+  }
+#pragma unroll
+  for (int u = 0; u < 16; ++u)
+    if (u < G && u * KP + grp < cn && vj[u] == i) vq[u] = *reinterpret_cast<const uint4*>(own_v + gl * 8);
+  if (warp == 0 && blockIdx.y == 0 && h % (p.a.heads / p.a.kv_heads) == 0) {
+    T* kd = static_cast<T*>(p.kcache) + (int64_t)slot * p.k_slot_stride + (int64_t)i * krs + kvh * dim;
+    T* vd = static_cast<T*>(p.vcache) + (int64_t)slot * p.v_slot_stride + (int64_t)i * vrs + kvh * vdim;
+    for (int d = lane; d < dim; d += 32) kd[d] = own_k[d];
+    for (int d = lane; d < vdim; d += 32) vd[d] = own_v[d];
+  }
+  __syncthreads();
+  // ---- scores and the warp's softmax
+  float dot = 0.f;
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    if (u < nd8) {
+      float kf[8];
+      unpack8(kq[u], kf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot = fmaf(qs[u * 8 + e], kf[e], dot);
+    }
+  }
+  const float sc_ = valid ? dot * p.a.scale : -INFINITY;
+  const float m = warp_max(sc_);
+  const float pj = valid ? expf(sc_ - m) : 0.f;
+  const float l = warp_sum(pj);
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+  for (int u = 0; u < 16; ++u) {
+    const int src = u * KP + grp;
+    const float pw = __shfl_sync(0xffffffffu, pj, src & 31);
+    if (u < G && src < cn) {
+      float vf[8];
+      unpack8(vq[u], vf);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(pw, vf[e], acc[e]);
+    }
+  }
+  for (int off = G; off < 32; off <<= 1) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], off);
+  }
+  // ---- the four warps, then the splits
+  float* sc = smem_f + dim;                    // [4][2 + vdim]
+  float* mine = sc + warp * (2 + vdim);
+  if (lane == 0) {
+    mine[0] = m;
+    mine[1] = l;
+  }
+  if (lane < G) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) mine[2 + lane * 8 + e] = acc[e];
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  float mt = -INFINITY;
+  for (int w = 0; w < 4; ++w) mt = fmaxf(mt, sc[w * (2 + vdim)]);
+  float lt = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int w = 0; w < 4; ++w) {
+    const float* o = sc + w * (2 + vdim);
+    const float f = o[0] == -INFINITY ? 0.f : expf(o[0] - mt);
+    lt += o[1] * f;
+    if (lane < G) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] += o[2 + lane * 8 + e] * f;
+    }
+  }
+  float* o = p.split_ws + ((size_t)pair * p.nsplit + blockIdx.y) * (2 + vdim);
+  if (lane == 0) {
+    o[0] = mt;
+    o[1] = lt;
+  }
+  if (lane < G) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[2 + lane * 8 + e] = acc[e];
+  }
+  __threadfence();
+  __syncwarp();
+  unsigned int tk = 0;
+  if (lane == 0) tk = atomicAdd(p.split_tickets + pair, 1u);
+  tk = __shfl_sync(0xffffffffu, tk, 0);
+  if (tk != (unsigned int)p.nsplit - 1u) return;
+  if (lane == 0) p.split_tickets[pair] = 0;
+  __threadfence();
+  stack_attn_merge_pair<T>(p, pair, t, h, lane);
+}
+
 __global__ void __launch_bounds__(256) stack_bias_add_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ b,
                                                              int n, int64_t total) {
   pdl_trigger();
@@ -540,7 +697,12 @@ int launch_stack_rmsnorm(void* y, const float* x, const float* w, const int32_t*
 int launch_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int dim, float eps, float mult,
                          cudaStream_t st) {
   B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add: bad arguments");
-  B200_CUDA(launch_pdl(stack_rms_add_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x, y, w, dim, eps, mult));
+  if (rows <= 64 && dim <= 16 * 256)
+    B200_CUDA(launch_pdl(stack_rms_add_small_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x, y, w, dim,
+                         eps, mult));
+  else
+    B200_CUDA(launch_pdl(stack_rms_add_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x, y, w, dim, eps,
+                         mult));
   return B200_OK;
 }
 
@@ -666,6 +828,15 @@ int launch_stack_attention(const StackAttn& p, int dtype, cudaStream_t st) {
                    (!p.own_from_proj || (p.off_k % 8 == 0 && p.off_v % 8 == 0 && p.ld_proj % 8 == 0 &&
                                          (reinterpret_cast<uintptr_t>(p.proj) & 15) == 0)) &&
                    ((reinterpret_cast<uintptr_t>(p.kcache) | reinterpret_cast<uintptr_t>(p.vcache)) & 15) == 0;
+  if (vec && p.split_ws != nullptr && p.own_from_proj && p.a.dim <= 128 && (vd == 64 || vd == 128) &&
+      p.keys_per_split <= 128 && (int64_t)p.n_tok * p.a.heads * p.nsplit <= 2 * 148) {
+    // the decode shape, and few enough CTAs to be resident together (the prefetch costs 242 registers per thread: two
+    // CTAs per SM): cached rows requested ahead of the dependency wait
+    const dim3 grid((unsigned)((int64_t)p.n_tok * p.a.heads), (unsigned)p.nsplit);
+    const size_t smem = ((size_t)p.a.dim + 4 * (2 + (size_t)vd)) * sizeof(float);
+    B200_CUDA(launch_pdl(stack_attn_decode_kernel, grid, dim3(128), smem, st, stack_pdl(), p));
+    return B200_OK;
+  }
   if (dtype == B200_F32) {
     if (wide) B200_CUDA((launch_attn_t<float, 4, false>(p, st)));
     else B200_CUDA((launch_attn_t<float, 1, false>(p, st)));
