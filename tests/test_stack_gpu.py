@@ -323,6 +323,27 @@ def test_long_prompts_big_heads_and_split_keys(dtype, hd):
     eng.close()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_longer_than_one_pass_and_unordered_wants(dtype):
+    """A step of more rows than one pass through the layers takes (4 096) is cut by the engine; the rows around the cut
+    agree with the same prompt fed in two steps, and wanted places come back in the order they were asked for."""
+    cfg = so.make_config(width=32, vocab=50, side_dim=4, loop=(0, 1, 2),
+                         layers=[dict(heads=2, kv_heads=1, dim=8, vdim=8, size=16, keep_first=2, ff=16)])
+    w = so.make_weights(cfg, seed=30)
+    toks = tokens(4200, cfg["vocab"], 31)
+    want = [4199, 0, 4096, 4095, 4097, 17, 2100, 4094]
+    eng = make_engine(cfg, w, dtype, max_ctx=4300, max_slots=2)
+    one = eng.step([(0, toks, want)])
+    a = eng.step([(1, toks[:2100], [0, 17])])
+    b = eng.step([(1, toks[2100:], [k - 2100 for k in (4199, 4096, 4095, 4097, 2100, 4094)])])
+    two = torch.stack([b[0], a[0], b[1], b[2], b[3], a[1], b[4], b[5]])
+    assert rel_err(one, two) < (1e-5 if dtype == torch.float32 else 3e-2)
+    # the first rows also against the restatement
+    ref = so.forward(cfg, w, toks[:18])
+    assert rel_err(one[[1, 5]], ref[[0, 17]]) < TOL[dtype]
+    eng.close()
+
+
 def test_fast_products_agree_with_the_general_kernels(monkeypatch):
     """bf16: the GEMV / tcgen05 / tensor-core-attention routes against the same engine held on the general kernels
     (B200_STACK_PLAIN=1) — same rounding points up to summation order, so far tighter than against the fp32 restatement."""
