@@ -56,6 +56,23 @@ def test_struct_layouts_match_header(built_lib):
     assert _lib.IPC_HANDLE_BYTES == int(re.search(r"#define B200_IPC_HANDLE_BYTES (\d+)", HEADER).group(1))
 
 
+def test_stack_struct_layouts_match_the_compiler(built_lib, tmp_path):
+    """The layer-stack descriptors travel by value through ctypes: sizes and the offsets of their last fields must be what
+    a C compiler makes of the header."""
+    from tinygpt_b200 import _lib
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200_decode.h"\n'
+                   'int main(void) { printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(b200_attn_desc), sizeof(b200_stack_layer), '
+                   'sizeof(b200_stack_desc), offsetof(b200_stack_layer, side_norm), offsetof(b200_stack_desc, layers_host), '
+                   'offsetof(b200_stack_layer, w_out)); return 0; }\n')
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
+    want = [C.sizeof(_lib.AttnDesc), C.sizeof(_lib.StackLayer), C.sizeof(_lib.StackDesc), _lib.StackLayer.side_norm.offset,
+            _lib.StackDesc.layers_host.offset, _lib.StackLayer.w_out.offset]
+    assert got == want
+
+
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the no-GPU behaviour")
 def test_no_gpu_means_loud_failure_not_fallback(built_lib):
     from tinygpt_b200 import _lib, engine, models, ops
