@@ -33,7 +33,7 @@ extern "C" {
  * b200_engine_set_sampler, b200_engine_options;  4: + layer-stack models (b200_stack_desc, b200_engine_create_stack),
  * sequence slots and the ragged step (b200_engine_step, b200_engine_slot_*), the per-mechanism stack ops.  All additive:
  * callers of an older version keep working. */
-#define B200_ABI_VERSION 4
+#define B200_ABI_VERSION 5
 
 typedef enum b200_status {
   B200_OK = 0,
@@ -291,8 +291,19 @@ int64_t b200_engine_bytes_per_token(const b200_engine* eng, int64_t ctx);
  * residual are merged by columns into w_out = [o | ff down]; vectors (norm weights, biases) are fp32.
  * ---------------------------------------------------------------------------------------------------------------- */
 typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1 } b200_dtype;
-typedef enum b200_block_kind { B200_BLOCK_PARALLEL = 0 } b200_block_kind;
-typedef enum b200_ff_act { B200_ACT_GELU_TANH = 0, B200_ACT_SILU = 1 } b200_ff_act;
+/* PARALLEL: x += m·(mixer(h) + ff(h)), h = norm(x), one norm.  SANDWICH: x += post_norm(mixer(norm(x))), then
+ * x += ff_post_norm(ff(ff_norm(x))) — a norm before and after every sublayer. */
+typedef enum b200_block_kind { B200_BLOCK_PARALLEL = 0, B200_BLOCK_SANDWICH = 1 } b200_block_kind;
+typedef enum b200_ff_act { B200_ACT_GELU_TANH = 0, B200_ACT_SILU = 1, B200_ACT_GELU_ERF = 2 } b200_ff_act;
+/* RMS: x·rsqrt(mean(x²) + eps)·(offset + w).  LAYER: (x − mean)·rsqrt(var + eps)·(offset + w), no bias. */
+typedef enum b200_norm_kind { B200_NORM_RMS = 0, B200_NORM_LAYER = 1 } b200_norm_kind;
+/* ATTENTION: the gated windowed attention of b200_attn_desc.  LATENT: keys and values expanded from a cached low-rank
+ * latent + one rotated key part shared by the heads (b200_latent_desc).  MLSTM: a matrix memory per head carried from
+ * token to token (b200_mlstm_desc); its state lives in fp32 beside the slot's caches. */
+typedef enum b200_mixer_kind { B200_MIX_ATTENTION = 0, B200_MIX_LATENT = 1, B200_MIX_MLSTM = 2 } b200_mixer_kind;
+/* GATED: act(gate)·up → down (merged into w_in / w_out).  DENSE: act(up) → down.  MOE: routed clamped gated experts
+ * (+ optional gated shared expert), b200_moe_desc. */
+typedef enum b200_ff_kind { B200_FF_GATED = 0, B200_FF_DENSE = 1, B200_FF_MOE = 2 } b200_ff_kind;
 
 typedef struct b200_attn_desc {
   int32_t heads;       /* query heads */
@@ -305,12 +316,48 @@ typedef struct b200_attn_desc {
   int32_t out_gate;    /* 1: head output × sigmoid(gate logit of that head) */
 } b200_attn_desc;
 
+/* Latent attention (sizes heads / dim / vdim / scale in b200_attn_desc; kv_heads = 1, no window, no gate).  Per head the
+ * query is [dim plain | rot_dim rotated]; w_in rows are [q: heads·(dim + rot_dim) | down: kv_rank + rot_dim] (the down
+ * segment starts at off_k).  c = rms(down[:kv_rank])·c_norm is the latent, down[kv_rank:] rotated is the key part all
+ * heads share; the slot's cache row of a position is [c | rotated key part].  score = (q_plain·(uk_h c) + q_rot·k_rot)·scale,
+ * value = uv_h c; the engine folds uk_h into the query and uv_h behind the softmax, so only cache rows are read.
+ * Rotation: pair (2i, 2i+1) of the first rot_dims entries turns by the angle of rot_table[pos][i] = {cos, sin}·magnitude. */
+typedef struct b200_latent_desc {
+  int32_t kv_rank, rot_dim, rot_dims;
+  const float* c_norm;      /* [kv_rank] */
+  const void* uk_t;         /* [heads][kv_rank][dim]: uk of head h transposed */
+  const void* uv;           /* [heads·vdim][kv_rank] */
+  const float* rot_table;   /* [max_ctx][rot_dims/2][2] fp32 */
+} b200_latent_desc;
+
+/* mLSTM (sizes heads / dim / vdim in b200_attn_desc).  w_in rows [q | k | v | out gate: heads·vdim | gates: 2·heads] at
+ * off_q / off_k / off_v / off_g / off_gate; the gate rows (input-gate rows, then forget-gate rows, biases in b_in) give raw
+ * logits that are kept in fp32 and capped as cap·tanh(z/cap); i = capped, f = logsigmoid(capped); m_t = max(f + m, i),
+ * S_t = e^(f+m−m_t) S + e^(i−m_t) k vᵀ, n likewise, o = Sᵀq' / (max(|n·q'|, e^(−m_t)) + 1e-6) with q' = q·dim^(−1/2);
+ * then o/rms(o) per head · head_norm · sigmoid(out gate). */
+typedef struct b200_mlstm_desc {
+  float gate_cap;
+  const float* head_norm;   /* [heads·vdim] */
+} b200_mlstm_desc;
+
+/* Mixture of experts: scores = sigmoid(router·h) (fp32), the `top` largest are chosen, the chosen expert runs on score·h
+ * (the weight multiplies the expert's INPUT), outputs are summed.  Expert: g = min(gate·h, limit), u = clamp(up·h, ±limit),
+ * down·(g·sigmoid(1.702 g)·(u + 1)).  Shared expert (shared_ff > 0): the same form on h itself, times sigmoid(sg·h). */
+typedef struct b200_moe_desc {
+  int32_t experts, top, expert_ff, shared_ff;
+  float limit, shared_limit;
+  const void* router;       /* [experts, width] */
+  const void* w_exp_in;     /* [experts][2·expert_ff, width]: gate rows, then up rows */
+  const void* w_exp_out;    /* [experts][width, expert_ff] */
+} b200_moe_desc;
+
 typedef struct b200_stack_layer {
   b200_attn_desc attn;
   int32_t ff;          /* feed-forward width; 0 = the layer has none */
   int32_t ff_act;      /* b200_ff_act */
   int32_t off_q, off_k, off_v, off_g, off_gate, off_up, n_in; /* first row of each segment of w_in; n_in = all rows */
-  int32_t off_act, k_out; /* w_out columns: [0, heads·vdim) attention, [off_act, off_act + ff) feed-forward; k_out = all */
+  int32_t off_act, k_out; /* w_out columns: [0, heads·vdim) attention, [off_act, off_act + ff) feed-forward; k_out = all
+                           * (sandwich blocks: k_out = heads·vdim, the mixer alone) */
   const float* norm;   /* [width] */
   const void* w_in;    /* [n_in, width] */
   const float* b_in;   /* [n_in] (0 where a segment has no bias) or NULL */
@@ -319,6 +366,19 @@ typedef struct b200_stack_layer {
   const void* side_gate; /* [side_dim, width] or NULL: no side input */
   const void* side_proj; /* [width, side_dim] */
   const float* side_norm; /* [width] */
+  /* ---- sandwich blocks (zero / NULL for parallel blocks) */
+  int32_t mixer;         /* b200_mixer_kind */
+  int32_t ff_kind;       /* b200_ff_kind */
+  const float* post_norm;    /* [width] norm of the mixer's output */
+  const float* ff_norm;      /* [width] norm before the feed-forward */
+  const float* ff_post_norm; /* [width] norm of the feed-forward's output */
+  /* feed-forward of a sandwich block: DENSE w_ff_in [ff, width], w_ff_out [width, ff]; MOE with a shared expert:
+   * w_ff_in [up8(2·shared_ff + 1), width] = [gate | up | shared-gate logit row], w_ff_out [width, shared_ff] */
+  const void* w_ff_in;
+  const void* w_ff_out;
+  b200_latent_desc lat;
+  b200_mlstm_desc rec;
+  b200_moe_desc moe;
 } b200_stack_layer;
 
 typedef struct b200_stack_desc {
@@ -337,6 +397,8 @@ typedef struct b200_stack_desc {
   const float* final_norm; /* [width] */
   const void* head;      /* [vocab, width] */
   const b200_stack_layer* layers_host;
+  int32_t norm_kind;     /* b200_norm_kind of the block and final norms */
+  float logit_softcap;   /* > 0: logits <- cap·tanh(logits / cap) */
 } b200_stack_desc;
 
 /* Build a stack engine (single GPU).  Borrows the weights; owns the caches [slot][run][max_ctx][kv_heads·dim | ·vdim],
@@ -383,6 +445,30 @@ int b200_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, int6
 /* x[r,:] += mult · y[r,:] · rsqrt(mean(y[r,:]²) + eps) · w[:]   (all fp32) */
 int b200_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, int64_t dim, float eps, float mult,
                        void* stream);
+/* y[r,:] = T( norm(x[r,:]) · w ) with norm of b200_norm_kind `kind`, x fp32;  add != 0: xadd[r,:] += that (fp32, y unused) */
+int b200_stack_norm(void* y, float* xadd, const float* x, const float* w, int64_t rows, int64_t dim, float eps, int kind,
+                    int add, int dtype, void* stream);
+/* Latent attention over per-slot caches, everything between the in-projection and the out-projection: `proj` rows hold
+ * [q | down] (q at column 0, down at off_down); the cache rows [c | rotated key] of the new tokens are written, then every
+ * token attends to rows 0 … pos of its slot; out[t, h·vdim …] (row stride ld_out). */
+int b200_stack_latent_attention(void* out, int64_t ld_out, const void* proj, int64_t ld_proj, int64_t off_down, void* cache,
+                                int64_t slot_stride, const int32_t* slot, const int32_t* pos, int64_t n_tok,
+                                const b200_attn_desc* attn, const b200_latent_desc* lat, float eps, int dtype, void* stream);
+/* mLSTM recurrence of n_seq sequences laid side by side: sequence s brings rows [row0[s], row0[s] + count[s]) of `proj`
+ * (q | k | v at off_q / off_k / off_v) and `gates` (fp32 [rows, 2·heads] raw logits), continues the state of its slot
+ * (slot / pos are per ROW; a sequence whose first row has pos 0 starts from zero) and leaves it advanced.
+ * out fp32 [rows, heads, vdim + 2]: numerators Sᵀq', then n·q', then m.  State of a slot: b200_stack_mlstm_state_floats. */
+int b200_stack_mlstm(float* out, const void* proj, int64_t ld_proj, int64_t off_q, int64_t off_k, int64_t off_v,
+                     const float* gates, float* state, int64_t slot_stride, const int32_t* row0, const int32_t* count,
+                     const int32_t* slot, const int32_t* pos, int64_t n_seq, int64_t n_rows, const b200_attn_desc* sizes,
+                     float gate_cap, int dtype, void* stream);
+int64_t b200_stack_mlstm_state_floats(int64_t heads, int64_t dim, int64_t vdim);
+/* Routed experts on h [rows, width] (T): y fp32 [rows, width] = Σ_chosen expert_e(score_e · h); `chosen` (int32
+ * [rows, top]) and `scores` (fp32 [rows, top]) receive the routing when not NULL.  Synchronises (allocates its workspace). */
+int b200_stack_moe(float* y, const void* h, int64_t rows, int64_t width, const b200_moe_desc* moe, int32_t* chosen,
+                   float* scores, int dtype, void* stream);
+/* y[r, j] = T( min(g, limit)·sigmoid(1.702·min(g, limit))·(clamp(u, ±limit) + 1) ), g = gu[r, j], u = gu[r, n + j] */
+int b200_stack_glu_clamp(void* y, const void* gu, int64_t rows, int64_t n, float limit, int dtype, void* stream);
 
 /* ---- tensor parallel (one process per GPU; the caller exchanges the handles with torch.distributed) ---------- */
 

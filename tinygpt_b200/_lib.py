@@ -40,13 +40,32 @@ class AttnDesc(C.Structure):
                 ("scale", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("out_gate", C.c_int32)]
 
 
+class LatentDesc(C.Structure):
+    _fields_ = [("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
+                ("c_norm", C.c_void_p), ("uk_t", C.c_void_p), ("uv", C.c_void_p), ("rot_table", C.c_void_p)]
+
+
+class MlstmDesc(C.Structure):
+    _fields_ = [("gate_cap", C.c_float), ("head_norm", C.c_void_p)]
+
+
+class MoeDesc(C.Structure):
+    _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32),
+                ("limit", C.c_float), ("shared_limit", C.c_float),
+                ("router", C.c_void_p), ("w_exp_in", C.c_void_p), ("w_exp_out", C.c_void_p)]
+
+
 class StackLayer(C.Structure):
     _fields_ = [("attn", AttnDesc), ("ff", C.c_int32), ("ff_act", C.c_int32),
                 ("off_q", C.c_int32), ("off_k", C.c_int32), ("off_v", C.c_int32), ("off_g", C.c_int32),
                 ("off_gate", C.c_int32), ("off_up", C.c_int32), ("n_in", C.c_int32),
                 ("off_act", C.c_int32), ("k_out", C.c_int32),
                 ("norm", C.c_void_p), ("w_in", C.c_void_p), ("b_in", C.c_void_p), ("w_out", C.c_void_p),
-                ("side_col", C.c_int32), ("side_gate", C.c_void_p), ("side_proj", C.c_void_p), ("side_norm", C.c_void_p)]
+                ("side_col", C.c_int32), ("side_gate", C.c_void_p), ("side_proj", C.c_void_p), ("side_norm", C.c_void_p),
+                ("mixer", C.c_int32), ("ff_kind", C.c_int32),
+                ("post_norm", C.c_void_p), ("ff_norm", C.c_void_p), ("ff_post_norm", C.c_void_p),
+                ("w_ff_in", C.c_void_p), ("w_ff_out", C.c_void_p),
+                ("lat", LatentDesc), ("rec", MlstmDesc), ("moe", MoeDesc)]
 
 
 class StackDesc(C.Structure):
@@ -57,7 +76,8 @@ class StackDesc(C.Structure):
                 ("norm_offset", C.c_float), ("side_dim", C.c_int32), ("side_stride", C.c_int32),
                 ("max_ctx", C.c_int32), ("max_slots", C.c_int32),
                 ("embed", C.c_void_p), ("mix_in", C.c_void_p), ("side_table", C.c_void_p), ("final_norm", C.c_void_p),
-                ("head", C.c_void_p), ("layers_host", C.POINTER(StackLayer))]
+                ("head", C.c_void_p), ("layers_host", C.POINTER(StackLayer)),
+                ("norm_kind", C.c_int32), ("logit_softcap", C.c_float)]
 
 
 # name -> (restype, argtypes); every symbol include/b200_decode.h declares (tests/test_abi.py checks the two agree)
@@ -110,6 +130,13 @@ PROTOTYPES = {
     "b200_stack_kv_store": (I32, [P, P, I64, I64, P, I64, I64, I64, P, P, I64, C.POINTER(AttnDesc), I32, P]),
     "b200_stack_act_mul": (I32, [P, I64, P, P, I64, I64, I64, I32, I32, P]),
     "b200_stack_rms_add": (I32, [P, P, P, I64, I64, F, F, P]),
+    "b200_stack_norm": (I32, [P, P, P, P, I64, I64, F, I32, I32, I32, P]),
+    "b200_stack_latent_attention": (I32, [P, I64, P, I64, I64, P, I64, P, P, I64, C.POINTER(AttnDesc),
+                                          C.POINTER(LatentDesc), F, I32, P]),
+    "b200_stack_mlstm": (I32, [P, P, I64, I64, I64, I64, P, P, I64, P, P, P, P, I64, I64, C.POINTER(AttnDesc), F, I32, P]),
+    "b200_stack_mlstm_state_floats": (I64, [I64, I64, I64]),
+    "b200_stack_moe": (I32, [P, P, I64, I64, C.POINTER(MoeDesc), P, P, I32, P]),
+    "b200_stack_glu_clamp": (I32, [P, P, I64, I64, F, I32, P]),
     "b200_tp_window_bytes": (I64, [C.POINTER(ModelDesc)]),
     "b200_tp_window_create": (I32, [I64, C.POINTER(P), C.c_char_p]),
     "b200_tp_window_open": (I32, [C.c_char_p, C.POINTER(P)]),

@@ -1,5 +1,7 @@
 // api.cu — C-ABI entry points for the GEMV and the fused building blocks (declared in include/b200_decode.h).
 #include "gemv.cuh"
+#include "stack_mix.cuh"
+#include <vector>
 #include "ops.cuh"
 #include "stack.cuh"
 
@@ -180,6 +182,109 @@ int b200_stack_rms_add(float* x, const float* y, const float* w, int64_t rows, i
   if (rc != B200_OK) return rc;
   B200_CHECK_ARG(dim > 0 && dim < (1ll << 31) && rows < (1ll << 31), "stack_rms_add: size out of range");
   return b200::launch_stack_rms_add(x, y, w, rows, (int)dim, eps, mult, (cudaStream_t)stream);
+}
+
+// ---- mechanisms of sandwich blocks (stack_mix.cu).  The ops that need scratch allocate it, run and synchronise.
+namespace {
+struct Scratch {
+  std::vector<void*> ptrs;
+  void* take(size_t bytes) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, bytes > 0 ? bytes : 1) != cudaSuccess) return nullptr;
+    cudaMemset(p, 0, bytes > 0 ? bytes : 1);
+    ptrs.push_back(p);
+    return p;
+  }
+  ~Scratch() {
+    cudaDeviceSynchronize();
+    for (void* p : ptrs) cudaFree(p);
+  }
+};
+}  // namespace
+
+int b200_stack_norm(void* y, float* xadd, const float* x, const float* w, int64_t rows, int64_t dim, float eps, int kind,
+                    int add, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(dim > 0 && dim < (1ll << 31) && rows > 0 && rows < (1ll << 31), "stack_norm: size out of range");
+  if (add) return b200::launch_stack_norm_add(xadd, x, false, w, rows, (int)dim, eps, 1.f, kind, (cudaStream_t)stream);
+  return b200::launch_stack_norm(y, x, w, nullptr, rows, (int)dim, eps, 0.f, kind, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_latent_attention(void* out, int64_t ld_out, const void* proj, int64_t ld_proj, int64_t off_down, void* cache,
+                                int64_t slot_stride, const int32_t* slot, const int32_t* pos, int64_t n_tok,
+                                const b200_attn_desc* attn, const b200_latent_desc* lat, float eps, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(attn && lat && n_tok > 0 && n_tok < (1 << 24), "stack_latent_attention: bad arguments");
+  B200_CHECK_ARG(dtype == B200_BF16 || dtype == B200_F32, "stack_latent_attention: unknown dtype");
+  const size_t esz = dtype == B200_F32 ? 4 : 2;
+  Scratch sc;
+  b200::LatentRun p;
+  p.a = *attn; p.l = *lat; p.eps = eps;
+  p.proj = proj; p.ld_proj = ld_proj; p.off_q = 0; p.off_down = (int)off_down;
+  p.cache = cache; p.slot_stride = slot_stride; p.slot = slot; p.pos = pos; p.n_tok = (int)n_tok;
+  p.qa = sc.take((size_t)n_tok * attn->heads * (lat->kv_rank + lat->rot_dim) * esz);
+  p.ol = sc.take((size_t)n_tok * attn->heads * lat->kv_rank * esz);
+  B200_CHECK_ARG(p.qa && p.ol, "stack_latent_attention: out of device memory");
+  p.out = out; p.ld_out = ld_out;
+  return b200::run_latent_attention(p, dtype, (cudaStream_t)stream);
+}
+
+int b200_stack_mlstm(float* out, const void* proj, int64_t ld_proj, int64_t off_q, int64_t off_k, int64_t off_v,
+                     const float* gates, float* state, int64_t slot_stride, const int32_t* row0, const int32_t* count,
+                     const int32_t* slot, const int32_t* pos, int64_t n_seq, int64_t n_rows, const b200_attn_desc* sizes,
+                     float gate_cap, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(sizes && n_seq > 0 && n_rows >= n_seq && n_rows < (1 << 24), "stack_mlstm: bad arguments");
+  b200::MlstmRun p;
+  p.a = *sizes; p.gate_cap = gate_cap;
+  p.proj = proj; p.ld_proj = ld_proj; p.off_q = (int)off_q; p.off_k = (int)off_k; p.off_v = (int)off_v;
+  p.gates = gates; p.ld_gates = 2 * sizes->heads;
+  p.state = state; p.slot_stride = slot_stride;
+  p.seg_row0 = row0; p.seg_count = count; p.slot = slot; p.pos = pos; p.n_seg = (int)n_seq; p.n_tok = (int)n_rows;
+  p.o = out;
+  return b200::run_mlstm(p, dtype, (cudaStream_t)stream);
+}
+
+int64_t b200_stack_mlstm_state_floats(int64_t heads, int64_t dim, int64_t vdim) {
+  return b200::mlstm_state_floats((int)heads, (int)dim, (int)vdim);
+}
+
+int b200_stack_moe(float* y, const void* h, int64_t rows, int64_t width, const b200_moe_desc* moe, int32_t* chosen,
+                   float* scores, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(moe && rows > 0 && rows < (1 << 22) && width > 0 && width < (1 << 24) && moe->top > 0 && moe->experts > 0,
+                 "stack_moe: bad arguments");
+  B200_CHECK_ARG(dtype == B200_BF16 || dtype == B200_F32, "stack_moe: unknown dtype");
+  const size_t esz = dtype == B200_F32 ? 4 : 2, P = (size_t)rows * moe->top;
+  Scratch sc;
+  b200::MoeRun p;
+  p.m = *moe; p.width = (int)width; p.n_tok = (int)rows; p.h = h; p.y = y;
+  p.z = (float*)sc.take((size_t)rows * moe->experts * 4);
+  p.sel_e = (int32_t*)sc.take(P * 4);
+  p.sel_w = (float*)sc.take(P * 4);
+  p.plan = (int32_t*)sc.take((size_t)b200::moe_plan_ints((int)P, moe->experts) * 4);
+  p.pair_slot = (int32_t*)sc.take(P * 4);
+  p.a_perm = sc.take(P * width * esz);
+  p.gu = sc.take(P * 2 * moe->expert_ff * esz);
+  p.act = sc.take(P * moe->expert_ff * esz);
+  p.outp = (float*)sc.take(P * width * 4);
+  B200_CHECK_ARG(p.z && p.sel_e && p.sel_w && p.plan && p.pair_slot && p.a_perm && p.gu && p.act && p.outp,
+                 "stack_moe: out of device memory");
+  if ((rc = b200::run_moe(p, dtype, (cudaStream_t)stream)) != B200_OK) return rc;
+  if (chosen) B200_CUDA(cudaMemcpyAsync(chosen, p.sel_e, P * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  if (scores) B200_CUDA(cudaMemcpyAsync(scores, p.sel_w, P * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  return B200_OK;
+}
+
+int b200_stack_glu_clamp(void* y, const void* gu, int64_t rows, int64_t n, float limit, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(n > 0 && n < (1ll << 30) && rows > 0, "stack_glu_clamp: size out of range");
+  return b200::launch_stack_glu_clamp(y, n, gu, 2 * n, rows, (int)n, limit, dtype, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -13,7 +13,19 @@
 //   mid[:, off_act …)       = act(ff gate)·ff up
 //   x   += m · mid·w_outᵀ                      ONE product for o | ff down, summed in fp32 straight into the stream
 //   x   += m · rmsnorm(side_proj·(gelu(side_gate·x) ∘ table[token]))·w_side
-// then rmsnorm of the wanted rows only and the head product (fp32 logits + the bf16 copy argmax / sampler read).
+// then the final norm of the wanted rows only and the head product (fp32 logits + the bf16 copy argmax / sampler read).
+//
+// Per run of a layer (sandwich block: a norm before and after each sublayer; norms of either kind):
+//   h    = norm(x)·w                            fp32 → T
+//   proj = h·w_inᵀ + b_in                       the mixer's in-projections in one product
+//   mid  = latent attention(proj, cache)        cache row of a position = [latent | rotated shared key part]
+//        | mLSTM(proj, fp32 gate logits, state) state of a run = fp32 matrix memory per head, carried in the slot
+//   x   += norm(mid·w_outᵀ)·post_norm
+//   h    = norm(x)·ff_norm
+//   y    = w_ff_out·act(w_ff_in·h)              dense, or
+//        | Σ_chosen expert(score·h) + sigmoid(sg·h)·shared(h)    routed experts: rows sorted by expert, grouped products
+//   x   += norm(y)·ff_post_norm
+// and the logits may be soft-capped.
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -21,6 +33,7 @@
 #include <vector>
 
 #include "engine.cuh"
+#include "stack_mix.cuh"
 
 namespace b200 {
 
@@ -87,7 +100,26 @@ struct StackEngine {
   // graph outlives changes of the active set); dropped when the workspace moves
   std::map<int, cudaGraphExec_t> g_dec;
   std::map<int, int> g_launches_of;
+  // ---- sandwich blocks
+  // recurrent state (mLSTM runs): fp32 [slot][run's share]; a sequence at position 0 starts from zero, so a slot that is
+  // given back needs no clearing
+  float* rstate = nullptr;
+  std::vector<size_t> run_s_off;   // floats from the start of a slot
+  size_t s_slot = 0;               // floats per slot
+  bool recurrent = false;          // some run carries state that cannot be rewound
+  void *qa = nullptr, *ol = nullptr, *lin_tmp = nullptr;
+  float *projf = nullptr, *rec_o = nullptr, *y2 = nullptr;
+  int32_t *m_seg_row0 = nullptr, *m_seg_count = nullptr;
+  MoeRun moe_ws{};                 // the routing workspace's pointers
+  int qa_max = 0, ol_max = 0, rec_o_max = 0, moe_e_max = 0, moe_top_max = 0, moe_ff_max = 0, lin_max = 0;
+  bool any_rec = false, any_moe = false;
+  struct SPlans {
+    GemvPlan in{}, out{}, ff_in{}, ff_out{};
+    bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false;
+  };
+  std::vector<SPlans> splans;
 };
+static inline int up8i(int n) { return (n + 7) / 8 * 8; }
 constexpr int kGemmRows = 32;
 
 namespace {
@@ -157,10 +189,22 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_mid = take(T * s->k_out_max * s->esz), o_sg = take(T * std::max(1, d.side_dim) * s->esz);
   const size_t o_hn = take((size_t)rows * W * s->esz), o_lg = take((size_t)rows * d.vocab * 4);
   const size_t o_lb = take((size_t)rows * d.vocab * 2);
-  const size_t o_meta = take((3 * T + rows + 2 * (size_t)d.max_slots) * 4);
+  const size_t o_meta = take((5 * T + rows + 2 * (size_t)d.max_slots) * 4);
   const size_t o_cat = take(d.mix_in != nullptr && s->dtype == B200_BF16 ? T * 2 * W * 2 : 0);
   const size_t o_aws = take((size_t)kStackSplitRows * s->max_heads * kStackMaxSplits * (2 + s->max_vdim) * 4);
   const size_t o_tick = take((size_t)kStackSplitRows * s->max_heads * 4);
+  // sandwich blocks
+  const bool sw = d.block == B200_BLOCK_SANDWICH;
+  const size_t o_qa = take(sw ? T * s->qa_max * s->esz : 0), o_ol = take(sw ? T * s->ol_max * s->esz : 0);
+  const size_t o_lt = take(sw ? T * s->lin_max * 2 : 0);
+  const size_t o_pf = take(s->any_rec ? (size_t)kMaxBatch * s->n_in_max * 4 + T * 2 * s->max_heads * 4 : 0);
+  const size_t o_ro = take(s->any_rec ? T * s->rec_o_max * 4 : 0), o_y2 = take(sw ? T * W * 4 : 0);
+  const size_t P = T * std::max(1, s->moe_top_max);
+  const size_t o_mz = take(s->any_moe ? T * s->moe_e_max * 4 : 0), o_me = take(s->any_moe ? P * 4 : 0);
+  const size_t o_mw = take(s->any_moe ? P * 4 : 0), o_mp = take(s->any_moe ? (size_t)moe_plan_ints((int)P, s->moe_e_max) * 4 : 0);
+  const size_t o_ms = take(s->any_moe ? P * 4 : 0), o_ma = take(s->any_moe ? P * W * s->esz : 0);
+  const size_t o_mg = take(s->any_moe ? P * 2 * s->moe_ff_max * s->esz : 0), o_mc = take(s->any_moe ? P * s->moe_ff_max * s->esz : 0);
+  const size_t o_mo = take(s->any_moe ? P * W * 4 : 0);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->ws_tok = tok;
@@ -181,6 +225,23 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->m_pos = s->m_slot + T;
   s->m_want = s->m_pos + T;
   s->m_upd = s->m_want + rows;
+  s->m_seg_row0 = s->m_upd + 2 * (size_t)d.max_slots;
+  s->m_seg_count = s->m_seg_row0 + T;
+  s->qa = s->ws + o_qa;
+  s->ol = s->ws + o_ol;
+  s->lin_tmp = s->ws + o_lt;
+  s->projf = (float*)(s->ws + o_pf);
+  s->rec_o = (float*)(s->ws + o_ro);
+  s->y2 = (float*)(s->ws + o_y2);
+  s->moe_ws.z = (float*)(s->ws + o_mz);
+  s->moe_ws.sel_e = (int32_t*)(s->ws + o_me);
+  s->moe_ws.sel_w = (float*)(s->ws + o_mw);
+  s->moe_ws.plan = (int32_t*)(s->ws + o_mp);
+  s->moe_ws.pair_slot = (int32_t*)(s->ws + o_ms);
+  s->moe_ws.a_perm = s->ws + o_ma;
+  s->moe_ws.gu = s->ws + o_mg;
+  s->moe_ws.act = s->ws + o_mc;
+  s->moe_ws.outp = (float*)(s->ws + o_mo);
   s->cat = (__nv_bfloat16*)(s->ws + o_cat);
   s->attn_ws = (float*)(s->ws + o_aws);
   s->attn_tickets = (unsigned int*)(s->ws + o_tick);
@@ -273,7 +334,8 @@ static int stack_product_mix(StackEngine* s, const float* cur, float* other, int
 static int stack_product_head(StackEngine* s, const float* x, const int32_t* rows, int n_rows, cudaStream_t st) {
   const b200_stack_desc& d = s->d;
   int rc;
-  if (s->fast && n_rows <= kMaxBatch && s->ok_head && rows == nullptr) {   // the final norm is the GEMV's prologue
+  const int64_t n_lg = (int64_t)n_rows * d.vocab;
+  if (s->fast && n_rows <= kMaxBatch && s->ok_head && rows == nullptr && d.norm_kind == B200_NORM_RMS) {   // the final norm is the GEMV's prologue
     GemvPlan pl = s->p_head_f;
     pl.p.xf = x;
     pl.p.fnorm_w = d.final_norm;
@@ -282,10 +344,11 @@ static int stack_product_head(StackEngine* s, const float* x, const int32_t* row
     pl.p.y = s->logits_bf;
     pl.p.yf = s->logits;
     if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
-    return gemv_launch(pl, st, false);   // copies and the argmax follow: a full dependency
+    if ((rc = gemv_launch(pl, st, false)) != B200_OK) return rc;   // copies and the argmax follow: a full dependency
+    return d.logit_softcap > 0.f ? launch_stack_softcap(s->logits, s->logits_bf, n_lg, d.logit_softcap, st) : B200_OK;
   }
-  if ((rc = launch_stack_rmsnorm(s->hn, x, d.final_norm, rows, n_rows, d.width, d.norm_eps, d.norm_offset, s->dtype, st)) !=
-      B200_OK)
+  if ((rc = launch_stack_norm(s->hn, x, d.final_norm, rows, n_rows, d.width, d.norm_eps, d.norm_offset, d.norm_kind, s->dtype,
+                              st)) != B200_OK)
     return rc;
   if (s->fast && n_rows <= kMaxBatch && s->ok_head) {
     GemvPlan pl = s->p_head;
@@ -293,12 +356,13 @@ static int stack_product_head(StackEngine* s, const float* x, const int32_t* row
     pl.p.y = s->logits_bf;
     pl.p.yf = s->logits;
     if ((rc = gemv_plan_set_batch(&pl, n_rows)) != B200_OK) return rc;
-    return gemv_launch(pl, st, false);   // copies and the argmax follow: a full dependency
+    if ((rc = gemv_launch(pl, st, false)) != B200_OK) return rc;   // copies and the argmax follow: a full dependency
+    return d.logit_softcap > 0.f ? launch_stack_softcap(s->logits, s->logits_bf, n_lg, d.logit_softcap, st) : B200_OK;
   }
   StackGemm g;
   g.a = s->hn; g.lda = d.width; g.k1 = d.width;
   g.w = d.head; g.M = n_rows; g.N = d.vocab; g.K = d.width;
-  g.epi = SEPI_LOGITS; g.c = s->logits; g.ldc = d.vocab; g.c2 = s->logits_bf;
+  g.epi = SEPI_LOGITS; g.c = s->logits; g.ldc = d.vocab; g.c2 = s->logits_bf; g.softcap = d.logit_softcap;
   return launch_stack_gemm(g, s->dtype, st);
 }
 
@@ -399,6 +463,136 @@ static int stack_side(StackEngine* s, int li, float* cur, int n_tok, cudaStream_
   return launch_stack_rms_add(cur, s->y, L.side_norm, n_tok, W, d.norm_eps, d.residual_mult, st);
 }
 
+
+// ---------------------------------------------------------------------------------------------------- sandwich blocks
+// C = A·Wᵀ + bias for dense T-typed rows A [M, K]: out_t (T [M, N]) and / or out_f (fp32 [M, N]).  bf16 engines stream W
+// once for steps of up to kMaxBatch rows (GEMV; both outputs from the same fp32 sums), use the tcgen05 GEMM from kGemmRows
+// rows on (bf16 out, widened when fp32 is asked for), and the general kernel otherwise.
+static int stack_lin(StackEngine* s, const void* A, const void* Wt, const float* bias, int M, int N, int K, const GemvPlan* plan,
+                     void* out_t, float* out_f, cudaStream_t st) {
+  int rc;
+  if (s->fast && M <= kMaxBatch && plan != nullptr) {
+    GemvPlan pl = *plan;
+    pl.p.x = (const __nv_bfloat16*)A;
+    pl.p.y = (__nv_bfloat16*)(out_t ? out_t : s->lin_tmp);
+    pl.p.yf = out_f;
+    pl.p.fbias = bias;
+    if ((rc = gemv_plan_set_batch(&pl, M)) != B200_OK) return rc;
+    return gemv_launch(pl, st, s->pdl);
+  }
+  if (s->fast && M >= kGemmRows && gemm_shape_ok(N, K)) {
+    __nv_bfloat16* o = (__nv_bfloat16*)(out_t ? out_t : s->lin_tmp);
+    if ((rc = launch_gemm_bf16(o, A, Wt, M, N, K, st)) != B200_OK) return rc;
+    if (bias && (rc = launch_stack_bias_add(o, bias, M, N, st)) != B200_OK) return rc;
+    return out_f ? launch_stack_axpy(out_f, o, 1.f, false, (int64_t)M * N, st) : B200_OK;
+  }
+  StackGemm g;
+  g.a = A; g.lda = K; g.k1 = K;
+  g.w = Wt; g.bias = bias; g.M = M; g.N = N; g.K = K;
+  if (out_t) {
+    g.epi = SEPI_STORE; g.c = out_t; g.ldc = N;
+    if ((rc = launch_stack_gemm(g, s->dtype, st)) != B200_OK) return rc;
+  }
+  if (out_f) {
+    g.epi = SEPI_STORE_F32; g.c = out_f; g.ldc = N;
+    if ((rc = launch_stack_gemm(g, s->dtype, st)) != B200_OK) return rc;
+  }
+  return B200_OK;
+}
+
+// x += norm(A·Wᵀ)·w  — a sublayer's out-projection, its post-norm and the residual sum (fp32)
+static int stack_lin_norm_add(StackEngine* s, const void* A, const void* Wt, int M, int K, const GemvPlan* plan,
+                              const float* norm_w, float* x, cudaStream_t st) {
+  const b200_stack_desc& d = s->d;
+  const int W = d.width;
+  int rc;
+  if (s->fast && !(M <= kMaxBatch && plan != nullptr) && M >= kGemmRows && gemm_shape_ok(W, K)) {
+    if ((rc = launch_gemm_bf16(s->lin_tmp, A, Wt, M, W, K, st)) != B200_OK) return rc;
+    return launch_stack_norm_add(x, s->lin_tmp, true, norm_w, M, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+  }
+  if ((rc = stack_lin(s, A, Wt, nullptr, M, W, K, plan, nullptr, s->y, st)) != B200_OK) return rc;
+  return launch_stack_norm_add(x, s->y, false, norm_w, M, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+}
+
+static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaStream_t st) {
+  const b200_stack_desc& d = s->d;
+  const int li = s->run_layer[r];
+  const b200_stack_layer& L = s->layers[li];
+  const StackEngine::SPlans& pl = s->splans[li];
+  const int W = d.width, dt = s->dtype;
+  const size_t esz = s->esz;
+  int rc;
+  // ---- mixer
+  if ((rc = launch_stack_norm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
+    return rc;
+  const bool rec = L.mixer == B200_MIX_MLSTM;
+  const bool gemv_in = s->fast && n_tok <= kMaxBatch && pl.ok_in;
+  // an mLSTM's gate logits stay fp32: the GEMV hands out its unrounded sums, the other paths run the gate rows again
+  if ((rc = stack_lin(s, s->h, L.w_in, L.b_in, n_tok, L.n_in, W, pl.ok_in ? &pl.in : nullptr, s->proj,
+                      rec && gemv_in ? s->projf : nullptr, st)) != B200_OK)
+    return rc;
+  if (L.mixer == B200_MIX_LATENT) {
+    LatentRun a;
+    a.a = L.attn; a.l = L.lat; a.eps = d.norm_eps;
+    a.proj = s->proj; a.ld_proj = L.n_in; a.off_q = L.off_q; a.off_down = L.off_k;
+    a.cache = s->kbase + s->run_k_off[r] * esz; a.slot_stride = (int64_t)s->k_slot;
+    a.slot = s->m_slot; a.pos = s->m_pos; a.n_tok = n_tok;
+    a.qa = s->qa; a.ol = s->ol; a.out = s->mid; a.ld_out = L.k_out;
+    if ((rc = run_latent_attention(a, dt, st)) != B200_OK) return rc;
+  } else {
+    const int H = L.attn.heads;
+    MlstmRun m;
+    m.a = L.attn; m.gate_cap = L.rec.gate_cap; m.eps = d.norm_eps;
+    m.proj = s->proj; m.ld_proj = L.n_in; m.off_q = L.off_q; m.off_k = L.off_k; m.off_v = L.off_v; m.off_g = L.off_g;
+    if (gemv_in) {
+      m.gates = s->projf + L.off_gate; m.ld_gates = L.n_in;
+    } else {
+      float* gates = s->projf + (size_t)kMaxBatch * s->n_in_max;
+      StackGemm g;
+      g.a = s->h; g.lda = W; g.k1 = W;
+      g.w = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz; g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
+      g.M = n_tok; g.N = 2 * H; g.K = W; g.epi = SEPI_STORE_F32; g.c = gates; g.ldc = 2 * H;
+      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      m.gates = gates; m.ld_gates = 2 * H;
+    }
+    m.state = s->rstate + s->run_s_off[r]; m.slot_stride = (int64_t)s->s_slot;
+    m.slot = s->m_slot; m.pos = s->m_pos; m.n_tok = n_tok;
+    if (s->segs.empty()) {
+      m.n_seg = n_tok;
+    } else {
+      m.n_seg = (int)s->segs.size(); m.seg_row0 = s->m_seg_row0; m.seg_count = s->m_seg_count;
+    }
+    m.o = s->rec_o; m.head_norm = L.rec.head_norm; m.mid = s->mid; m.ld_mid = L.k_out;
+    if ((rc = run_mlstm(m, dt, st)) != B200_OK) return rc;
+  }
+  if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x, st)) != B200_OK)
+    return rc;
+  // ---- feed-forward
+  if (L.ff_kind == B200_FF_DENSE && L.ff <= 0) return B200_OK;
+  if ((rc = launch_stack_norm(s->h, x, L.ff_norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
+    return rc;
+  if (L.ff_kind == B200_FF_DENSE) {
+    if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, L.ff, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
+      return rc;
+    if ((rc = launch_stack_act_mul(s->mid, L.ff, s->proj, nullptr, L.ff, n_tok, L.ff, L.ff_act, dt, st)) != B200_OK) return rc;
+    return stack_lin_norm_add(s, s->mid, L.w_ff_out, n_tok, L.ff, pl.ok_ff_out ? &pl.ff_out : nullptr, L.ff_post_norm, x, st);
+  }
+  MoeRun m = s->moe_ws;
+  m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
+  if (L.moe.shared_ff > 0) {
+    const int fs = L.moe.shared_ff, n_sh = up8i(2 * fs + 1);
+    if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, n_sh, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
+      return rc;
+    if ((rc = launch_stack_glu_clamp(s->mid, fs, s->proj, n_sh, n_tok, fs, L.moe.shared_limit, dt, st)) != B200_OK) return rc;
+    if ((rc = stack_lin(s, s->mid, L.w_ff_out, nullptr, n_tok, W, fs, pl.ok_ff_out ? &pl.ff_out : nullptr, nullptr, s->y2, st)) != B200_OK)
+      return rc;
+    m.shared = s->y2; m.shared_f32 = true;
+    m.sg = (const uint8_t*)s->proj + (size_t)2 * fs * esz; m.ld_sg = n_sh;
+  }
+  if ((rc = run_moe(m, dt, st)) != B200_OK) return rc;
+  return launch_stack_norm_add(x, s->y, false, L.ff_post_norm, n_tok, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+}
+
 // One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
 // rows_in_order: m_want is 0 … n_rows-1 (decode steps), so the head may read the stream directly.
 static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bool rows_in_order = false) {
@@ -409,8 +603,21 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bo
   if ((rc = launch_stack_embed(s->x, s->x0, d.embed, s->m_tok, n_tok, d.vocab, W, d.embed_scale, dt, st)) != B200_OK)
     return rc;
   float *cur = s->x, *other = s->x_alt;
+  if (s->any_rec && !s->segs.empty()) {   // the recurrences walk every sequence's rows in order
+    std::vector<int32_t> sr(2 * s->segs.size());
+    for (size_t i = 0; i < s->segs.size(); ++i) {
+      sr[i] = s->segs[i].row0;
+      sr[s->segs.size() + i] = s->segs[i].count;
+    }
+    B200_CUDA(cudaMemcpyAsync(s->m_seg_row0, sr.data(), s->segs.size() * 4, cudaMemcpyHostToDevice, st));
+    B200_CUDA(cudaMemcpyAsync(s->m_seg_count, sr.data() + s->segs.size(), s->segs.size() * 4, cudaMemcpyHostToDevice, st));
+  }
   for (int r = 0; r < d.n_runs; ++r) {
     const b200_stack_layer& L = s->layers[s->run_layer[r]];
+    if (d.block == B200_BLOCK_SANDWICH) {
+      if ((rc = stack_run_sandwich(s, r, cur, n_tok, st)) != B200_OK) return rc;
+      continue;
+    }
     if (s->run_mix[r]) {
       if ((rc = stack_product_mix(s, cur, other, n_tok, st)) != B200_OK) return rc;
       std::swap(cur, other);
@@ -494,6 +701,7 @@ void stack_destroy(b200_engine* e) {
   for (auto& kv : s->g_dec) cudaGraphExecDestroy(kv.second);
   if (s->cache) cudaFree(s->cache);
   if (s->state) cudaFree(s->state);
+  if (s->rstate) cudaFree(s->rstate);
   if (s->ws) cudaFree(s->ws);
   delete s;
   e->stack = nullptr;
@@ -520,6 +728,12 @@ int stack_seek(b200_engine* e, int64_t position, cudaStream_t st) {
   StackEngine* s = e->stack;
   // every slot of the active batch is rewound (they advance together under forward / decode)
   std::vector<int> slots = s->active.empty() ? std::vector<int>{0} : s->active;
+  if (s->recurrent)   // a recurrent state holds the whole prefix and nothing of its past
+    for (int sl : slots)
+      if (position != s->h_pos[sl] && position != 0) {
+        set_error("engine_seek: this model carries recurrent state; slot %d can only be rewound to position 0", sl);
+        return B200_ERR_UNSUPPORTED;
+      }
   for (int sl : slots)
     if (position < 0 || position > s->h_pos[sl]) {
       set_error("engine_seek: position %lld is not inside the cached prefix [0, %lld] of slot %d", (long long)position,
@@ -710,6 +924,16 @@ int64_t stack_bytes_per_token(const b200_engine* e, int64_t ctx) {
   for (int r = 0; r < d.n_runs; ++r) {
     const b200_stack_layer& L = s->layers[s->run_layer[r]];
     bytes += ((int64_t)L.n_in * d.width + (int64_t)d.width * L.k_out) * s->esz;
+    if (d.block == B200_BLOCK_SANDWICH) {
+      const b200_attn_desc& a = L.attn;
+      if (L.mixer == B200_MIX_LATENT)   // uk, uv, the cache rows read once and one written
+        bytes += ((int64_t)a.heads * (a.dim + a.vdim) * L.lat.kv_rank + (ctx + 2) * (L.lat.kv_rank + L.lat.rot_dim)) * s->esz;
+      else                              // the state read and written
+        bytes += 2 * mlstm_state_floats(a.heads, a.dim, a.vdim) * 4;
+      if (L.ff_kind == B200_FF_DENSE) bytes += 2ll * L.ff * d.width * s->esz;
+      else bytes += ((int64_t)L.moe.experts + 3ll * L.moe.top * L.moe.expert_ff + 3ll * L.moe.shared_ff + 1) * d.width * s->esz;
+      continue;
+    }
     if (s->run_mix[r]) bytes += 2ll * d.width * d.width * s->esz;
     if (L.side_gate) bytes += 2ll * d.side_dim * d.width * s->esz;
     int64_t keys = ctx + 1;
@@ -726,7 +950,13 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   if (rc != B200_OK) return rc;
   const b200_stack_desc& d = *desc;
   B200_CHECK_ARG(d.dtype == B200_BF16 || d.dtype == B200_F32, "engine_create_stack: unknown dtype %d", d.dtype);
-  B200_CHECK_ARG(d.block == B200_BLOCK_PARALLEL, "engine_create_stack: block kind %d not built", d.block);
+  B200_CHECK_ARG(d.block == B200_BLOCK_PARALLEL || d.block == B200_BLOCK_SANDWICH, "engine_create_stack: block kind %d not built",
+                 d.block);
+  B200_CHECK_ARG(d.norm_kind == B200_NORM_RMS || d.norm_kind == B200_NORM_LAYER, "engine_create_stack: norm kind %d not built",
+                 d.norm_kind);
+  B200_CHECK_ARG(d.block == B200_BLOCK_SANDWICH || d.norm_kind == B200_NORM_RMS,
+                 "engine_create_stack: parallel blocks are built with RMS norms");
+  B200_CHECK_ARG(d.logit_softcap >= 0.f, "engine_create_stack: negative logit_softcap");
   B200_CHECK_ARG(d.width > 0 && d.vocab > 0 && d.n_layers > 0 && d.n_runs > 0 && d.max_ctx > 0 && d.max_slots > 0,
                  "engine_create_stack: non-positive size");
   B200_CHECK_ARG(d.run_layer_host && d.run_mix_host && d.layers_host && d.embed && d.final_norm && d.head,
@@ -754,9 +984,65 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   s->run_mix.assign(d.run_mix_host, d.run_mix_host + d.n_runs);
   s->d.layers_host = nullptr;
   s->d.run_layer_host = s->d.run_mix_host = nullptr;
-  for (int l = 0; l < d.n_layers; ++l) {
+  const bool sandwich = d.block == B200_BLOCK_SANDWICH;
+  for (int l = 0; sandwich && l < d.n_layers; ++l) {
     const b200_stack_layer& L = s->layers[l];
     const b200_attn_desc& a = L.attn;
+    const int W = d.width;
+    B200_CHECK_ARG(L.mixer == B200_MIX_LATENT || L.mixer == B200_MIX_MLSTM, "engine_create_stack: layer %d: mixer kind %d is not built for sandwich blocks", l, L.mixer);
+    B200_CHECK_ARG(a.heads > 0 && a.dim > 0 && a.vdim > 0, "engine_create_stack: layer %d: bad mixer sizes", l);
+    B200_CHECK_ARG(L.norm && L.post_norm && L.w_in && L.w_out && L.n_in > 0 && L.k_out == a.heads * a.vdim,
+                   "engine_create_stack: layer %d: null weight or k_out != heads·vdim", l);
+    if (L.mixer == B200_MIX_LATENT) {
+      const b200_latent_desc& q = L.lat;
+      B200_CHECK_ARG(q.kv_rank > 0 && q.kv_rank <= kLatentMaxRank && q.rot_dim >= 0 && q.rot_dims >= 0 && q.rot_dims <= q.rot_dim &&
+                         q.rot_dims % 2 == 0,
+                     "engine_create_stack: layer %d: latent sizes (kv_rank 1 … %d, even rot_dims <= rot_dim)", l, kLatentMaxRank);
+      B200_CHECK_ARG(q.c_norm && q.uk_t && q.uv && (q.rot_dims == 0 || q.rot_table), "engine_create_stack: layer %d: null latent weight", l);
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * (a.dim + q.rot_dim) <= L.n_in && L.off_k >= 0 &&
+                         L.off_k + q.kv_rank + q.rot_dim <= L.n_in,
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      s->qa_max = std::max(s->qa_max, a.heads * (q.kv_rank + q.rot_dim));
+      s->ol_max = std::max(s->ol_max, a.heads * q.kv_rank);
+    } else {
+      B200_CHECK_ARG(a.dim <= kMlstmMaxDim && L.rec.gate_cap > 0.f && L.rec.head_norm, "engine_create_stack: layer %d: mLSTM description", l);
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.heads * a.dim <= L.n_in &&
+                         L.off_v + a.heads * a.vdim <= L.n_in && L.off_g + a.heads * a.vdim <= L.n_in &&
+                         L.off_gate + 2 * a.heads <= L.n_in,
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      s->rec_o_max = std::max(s->rec_o_max, a.heads * (a.vdim + 2));
+      s->any_rec = s->recurrent = true;
+    }
+    int ff_rows = 0, ff_mid = 0;
+    if (L.ff_kind == B200_FF_DENSE) {
+      B200_CHECK_ARG(L.ff >= 0 && (L.ff == 0 || (L.ff_norm && L.ff_post_norm && L.w_ff_in && L.w_ff_out)),
+                     "engine_create_stack: layer %d: dense feed-forward", l);
+      B200_CHECK_ARG(L.ff_act == B200_ACT_GELU_TANH || L.ff_act == B200_ACT_SILU || L.ff_act == B200_ACT_GELU_ERF,
+                     "engine_create_stack: layer %d: activation %d", l, L.ff_act);
+      ff_rows = ff_mid = L.ff;
+    } else {
+      const b200_moe_desc& m = L.moe;
+      B200_CHECK_ARG(L.ff_kind == B200_FF_MOE, "engine_create_stack: layer %d: feed-forward kind %d is not built for sandwich blocks", l, L.ff_kind);
+      B200_CHECK_ARG(m.experts > 0 && m.top > 0 && m.top <= m.experts && m.expert_ff > 0 && m.shared_ff >= 0 && m.router &&
+                         m.w_exp_in && m.w_exp_out && L.ff_norm && L.ff_post_norm && (m.shared_ff == 0 || (L.w_ff_in && L.w_ff_out)),
+                     "engine_create_stack: layer %d: mixture-of-experts description", l);
+      s->any_moe = true;
+      s->moe_e_max = std::max(s->moe_e_max, m.experts);
+      s->moe_top_max = std::max(s->moe_top_max, m.top);
+      s->moe_ff_max = std::max(s->moe_ff_max, m.expert_ff);
+      ff_rows = m.shared_ff > 0 ? up8i(2 * m.shared_ff + 1) : 0;
+      ff_mid = m.shared_ff;
+    }
+    s->max_heads = std::max(s->max_heads, a.heads);
+    s->n_in_max = std::max(s->n_in_max, std::max(L.n_in, ff_rows));
+    s->k_out_max = std::max(s->k_out_max, std::max(L.k_out, ff_mid));
+    s->lin_max = std::max(s->lin_max, std::max(W, std::max(L.n_in, ff_rows)));
+  }
+  for (int l = 0; !sandwich && l < d.n_layers; ++l) {
+    const b200_stack_layer& L = s->layers[l];
+    const b200_attn_desc& a = L.attn;
+    B200_CHECK_ARG(L.mixer == B200_MIX_ATTENTION && L.ff_kind == B200_FF_GATED,
+                   "engine_create_stack: layer %d: parallel blocks are built for attention mixers and gated feed-forwards", l);
     B200_CHECK_ARG(a.heads > 0 && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.dim > 0 && a.vdim > 0 && a.window >= 0 &&
                        a.keep_first >= 0,
                    "engine_create_stack: layer %d: bad attention sizes", l);
@@ -777,15 +1063,24 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   }
   s->run_k_off.resize(d.n_runs);
   s->run_v_off.resize(d.n_runs);
+  s->run_s_off.resize(d.n_runs);
   for (int r = 0; r < d.n_runs; ++r) {
     B200_CHECK_ARG(s->run_layer[r] >= 0 && s->run_layer[r] < d.n_layers, "engine_create_stack: run %d names layer %d", r,
                    s->run_layer[r]);
     B200_CHECK_ARG(!s->run_mix[r] || d.mix_in, "engine_create_stack: run %d mixes the embedding in but mix_in is null", r);
-    const b200_attn_desc& a = s->layers[s->run_layer[r]].attn;
+    const b200_stack_layer& RL = s->layers[s->run_layer[r]];
+    const b200_attn_desc& a = RL.attn;
     s->run_k_off[r] = s->k_slot;
     s->run_v_off[r] = s->v_slot;
-    s->k_slot += (size_t)d.max_ctx * a.kv_heads * a.dim;
-    s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
+    s->run_s_off[r] = s->s_slot;
+    if (RL.mixer == B200_MIX_ATTENTION) {
+      s->k_slot += (size_t)d.max_ctx * a.kv_heads * a.dim;
+      s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
+    } else if (RL.mixer == B200_MIX_LATENT) {   // one row per position: [latent | rotated shared key part]
+      s->k_slot += (size_t)d.max_ctx * (RL.lat.kv_rank + RL.lat.rot_dim);
+    } else {                                    // no rows per position: a fixed-size state
+      s->s_slot += (size_t)mlstm_state_floats(a.heads, a.dim, a.vdim);
+    }
   }
   B200_CUDA(cudaDeviceSynchronize());   // weights may still be in flight on the loader's stream
   {
@@ -802,7 +1097,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       if (k % 8 != 0 || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
       return gemv_make_plan(pl, w, n, n, k, 1, pro, epi, s->num_sms) == B200_OK;
     };
-    for (int l = 0; l < d.n_layers; ++l) {
+    for (int l = 0; !sandwich && l < d.n_layers; ++l) {
       const b200_stack_layer& L = s->layers[l];
       s->plans[l].ok_in = plan(&s->plans[l].in, L.w_in, L.n_in, d.width, EPI_BIAS_F32, PRO_F32);
       s->plans[l].ok_out = plan(&s->plans[l].out, L.w_out, d.width, L.k_out, EPI_RESID_F32);
@@ -810,14 +1105,33 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
                             plan(&s->plans[l].side_gate, L.side_gate, d.side_dim, d.width, EPI_ACT_TABLE, PRO_F32) &&
                             plan(&s->plans[l].side_proj, L.side_proj, d.width, d.side_dim, EPI_BIAS_F32);
     }
+    s->splans.resize(d.n_layers);
+    for (int l = 0; sandwich && l < d.n_layers; ++l) {
+      const b200_stack_layer& L = s->layers[l];
+      StackEngine::SPlans& sp = s->splans[l];
+      s->plans[l].ok_in = s->plans[l].ok_out = s->plans[l].ok_side = false;
+      sp.ok_in = plan(&sp.in, L.w_in, L.n_in, d.width, EPI_BIAS_F32);
+      sp.ok_out = plan(&sp.out, L.w_out, d.width, L.k_out, EPI_BIAS_F32);
+      if (L.ff_kind == B200_FF_DENSE && L.ff > 0) {
+        sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, L.ff, d.width, EPI_BIAS_F32);
+        sp.ok_ff_out = plan(&sp.ff_out, L.w_ff_out, d.width, L.ff, EPI_BIAS_F32);
+      } else if (L.ff_kind == B200_FF_MOE && L.moe.shared_ff > 0) {
+        sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, up8i(2 * L.moe.shared_ff + 1), d.width, EPI_BIAS_F32);
+        sp.ok_ff_out = plan(&sp.ff_out, L.w_ff_out, d.width, L.moe.shared_ff, EPI_BIAS_F32);
+      }
+    }
     if (d.mix_in) s->ok_mix = plan(&s->p_mix, d.mix_in, d.width, 2 * (int64_t)d.width, EPI_RESID_F32);
     s->ok_head = plan(&s->p_head, d.head, d.vocab, d.width, EPI_BIAS_F32) &&
                  plan(&s->p_head_f, d.head, d.vocab, d.width, EPI_BIAS_F32, PRO_F32);
   }
   const size_t kb = align_up(s->k_slot * d.max_slots * s->esz, 256), vb = align_up(s->v_slot * d.max_slots * s->esz, 256);
-  B200_CUDA(cudaMalloc((void**)&s->cache, kb + vb));
+  B200_CUDA(cudaMalloc((void**)&s->cache, std::max<size_t>(kb + vb, 256)));
   s->kbase = s->cache;
   s->vbase = s->cache + kb;
+  if (s->s_slot > 0) {
+    B200_CUDA(cudaMalloc((void**)&s->rstate, s->s_slot * d.max_slots * 4));
+    B200_CUDA(cudaMemset(s->rstate, 0, s->s_slot * d.max_slots * 4));
+  }
   size_t off = 0;
   auto take = [&](size_t bytes) {
     const size_t o = off;

@@ -36,6 +36,17 @@ struct StackGemm {
   const int32_t* tok = nullptr;
   int64_t table_ld = 0;
   int table_col = 0;
+  float softcap = 0.f;           // SEPI_LOGITS: > 0: acc <- cap·tanh(acc / cap) before it is stored
+  // batched: `batch` independent products, item b reads a + b·sa, w + b·sw and writes c + b·sc (elements)
+  int batch = 1;
+  int64_t sa = 0, sw = 0, sc = 0;
+  // grouped: the rows of A are sorted into groups, group e meets matrix w + e·sw.  The launch has n_tiles row tiles; tile i
+  // serves rows [tile_row0[i], min(tile_row0[i] + 64, group_end[e])) of group e = tile_group[i], or nothing (−1).  The
+  // three arrays live on the device (written by the routing kernels), so no step of this is decided on the host.
+  const int32_t* tile_group = nullptr;
+  const int32_t* tile_row0 = nullptr;
+  const int32_t* group_end = nullptr;
+  int n_tiles = 0;
 };
 int launch_stack_gemm(const StackGemm& g, int dtype, cudaStream_t st);
 

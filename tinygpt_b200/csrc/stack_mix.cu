@@ -1,0 +1,557 @@
+// stack_mix.cu — mixers and feed-forwards of sandwich blocks as plain kernels: any shape, storage type T = bf16 or fp32.
+// fp32 throughout for norms, the softmax, routing scores, the gates of the recurrence, the recurrence and its state.
+// Every kernel starts with griddepcontrol.launch_dependents + griddepcontrol.wait (programmatic dependent launch).
+#include "stack_mix.cuh"
+
+namespace b200 {
+
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ T cvt(float v);
+template <> __device__ __forceinline__ float cvt<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 cvt<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];
+  __syncthreads();
+  return tot;
+}
+
+inline int grid_cap(int64_t n, int block) {
+  int64_t g = (n + block - 1) / block;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(g, 148 * 16));
+}
+
+// --------------------------------------------------------------------------------------------------------- layer norm
+// One CTA per row.  mean, then the mean of squared deviations (two passes over the row, which stays in L1), then
+// (x − mean)·rsqrt(var + eps)·(offset + w): written as T, or added (× mult) into an fp32 stream.
+template <typename XT, typename YT, bool ADD>
+__global__ void __launch_bounds__(256) stack_layernorm_kernel(YT* __restrict__ y, float* __restrict__ xadd,
+                                                              const XT* __restrict__ x, const float* __restrict__ w,
+                                                              const int32_t* __restrict__ rows, int dim, float eps,
+                                                              float offset, float mult) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[8];
+  const int64_t src = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  const XT* xr = x + src * dim;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) s += ldf<XT>(xr + i);
+  const float mean = block_sum(s, red) / (float)dim;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float d = ldf<XT>(xr + i) - mean;
+    q += d * d;
+  }
+  const float inv = rsqrtf(block_sum(q, red) / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = (ldf<XT>(xr + i) - mean) * inv * (offset + w[i]);
+    if constexpr (ADD) xadd[(int64_t)blockIdx.x * dim + i] += mult * v;
+    else y[(int64_t)blockIdx.x * dim + i] = cvt<YT>(v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------- elementwise
+template <typename T>
+__global__ void __launch_bounds__(256) stack_glu_clamp_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ gu,
+                                                              int64_t ld_gu, int n, float limit, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / n;
+    const int j = (int)(e % n);
+    const float g = fminf(ldf<T>(gu + r * ld_gu + j), limit);
+    const float u = fminf(fmaxf(ldf<T>(gu + r * ld_gu + n + j), -limit), limit);
+    y[r * ld_y + j] = cvt<T>(g / (1.f + expf(-1.702f * g)) * (u + 1.f));
+  }
+}
+
+__global__ void __launch_bounds__(256) stack_softcap_kernel(float* __restrict__ lg, __nv_bfloat16* __restrict__ lb,
+                                                            int64_t total, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const float v = cap * tanhf(lg[e] / cap);
+    lg[e] = v;
+    if (lb != nullptr) lb[e] = __float2bfloat16_rn(v);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------- latent attention
+// One CTA per new token: the latent c = rms(down[:r])·c_norm and the rotated shared key part go into the slot's cache
+// row of the token's position; the rotated part of every head's query goes behind that head's folded query in qa.
+template <typename T>
+__global__ void __launch_bounds__(128) latent_prep_kernel(const LatentRun p) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[4];
+  const int t = blockIdx.x;
+  const int r = p.l.kv_rank, dr = p.l.rot_dim, kd = r + dr, dn = p.a.dim, half = p.l.rot_dims / 2;
+  const T* row = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  const T* down = row + p.off_down;
+  const int pos = p.pos[t];
+  T* crow = static_cast<T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride + (int64_t)pos * kd;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < r; i += blockDim.x) {
+    const float v = ldf<T>(down + i);
+    ss += v * v;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)r + p.eps);
+  for (int i = threadIdx.x; i < r; i += blockDim.x) crow[i] = cvt<T>(ldf<T>(down + i) * inv * p.l.c_norm[i]);
+  const float* cs = p.l.rot_table + (int64_t)pos * half * 2;
+  // rotated vectors: index 0 the shared key part, 1 … heads the queries' rotated parts
+  const int per = (dr + 1) / 2;   // pairs (the last one may be a single unrotated entry)
+  for (int e = threadIdx.x; e < (p.a.heads + 1) * per; e += blockDim.x) {
+    const int which = e / per, i = e % per;
+    const T* src = which == 0 ? down + r : row + p.off_q + (int64_t)(which - 1) * (dn + dr) + dn;
+    T* dst = which == 0 ? crow + r : static_cast<T*>(p.qa) + (int64_t)t * p.a.heads * kd + (int64_t)(which - 1) * kd + r;
+    const float u = ldf<T>(src + 2 * i);
+    if (2 * i + 1 >= dr) {
+      dst[2 * i] = cvt<T>(u);
+      continue;
+    }
+    const float v = ldf<T>(src + 2 * i + 1);
+    if (i < half) {
+      const float c = cs[2 * i], s = cs[2 * i + 1];
+      dst[2 * i] = cvt<T>(u * c - v * s);
+      dst[2 * i + 1] = cvt<T>(v * c + u * s);
+    } else {
+      dst[2 * i] = cvt<T>(u);
+      dst[2 * i + 1] = cvt<T>(v);
+    }
+  }
+}
+
+// One CTA of four warps per (token, head).  The query is [folded query (kv_rank) | rotated part]; key j is the cache row
+// [c_j | rotated key part], value j is c_j — the same row.  A warp walks keys 32 at a time: every key's dot product is
+// taken by the whole warp over the row's columns, lane l keeps the score of key l, the chunk joins an online softmax and
+// the rows are read once more as values.  The warps' partial softmaxes meet in shared memory.
+constexpr int kLatVR = kLatentMaxRank / 32;
+template <typename T>
+__global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float sm[];
+  const int t = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = p.l.kv_rank, kd = r + p.l.rot_dim;
+  float* q = sm;                 // [kd]
+  float* part = sm + kd;         // [4][2 + r]
+  const T* qrow = static_cast<const T*>(p.qa) + ((int64_t)t * p.a.heads + hd) * kd;
+  for (int i = threadIdx.x; i < kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
+  __syncthreads();
+  const int n_keys = p.pos[t] + 1;
+  const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
+  float m = -INFINITY, sum = 0.f, acc[kLatVR];
+#pragma unroll
+  for (int i = 0; i < kLatVR; ++i) acc[i] = 0.f;
+  for (int j0 = warp * 32; j0 < n_keys; j0 += 128) {
+    const int cnt = min(32, n_keys - j0);
+    float s_mine = -INFINITY;
+    for (int jj = 0; jj < cnt; ++jj) {
+      const T* kr = K + (int64_t)(j0 + jj) * kd;
+      float d = 0.f;
+      for (int i = lane; i < kd; i += 32) d = fmaf(q[i], ldf<T>(kr + i), d);
+      d = warp_sum(d);
+      if (lane == jj) s_mine = d;
+    }
+    const float m_new = fmaxf(m, warp_max(s_mine));
+    const float pr = lane < cnt ? expf(s_mine - m_new) : 0.f;
+    const float corr = expf(m - m_new);   // m = −inf on the first chunk: 0
+    sum = sum * corr + warp_sum(pr);
+#pragma unroll
+    for (int i = 0; i < kLatVR; ++i) acc[i] *= corr;
+    for (int jj = 0; jj < cnt; ++jj) {
+      const float pj = __shfl_sync(0xffffffffu, pr, jj);
+      const T* kr = K + (int64_t)(j0 + jj) * kd;
+#pragma unroll
+      for (int i = 0; i < kLatVR; ++i)
+        if (lane + 32 * i < r) acc[i] = fmaf(pj, ldf<T>(kr + lane + 32 * i), acc[i]);
+    }
+    m = m_new;
+  }
+  float* mine = part + warp * (2 + r);
+  if (lane == 0) {
+    mine[0] = m;
+    mine[1] = sum;
+  }
+#pragma unroll
+  for (int i = 0; i < kLatVR; ++i)
+    if (lane + 32 * i < r) mine[2 + lane + 32 * i] = acc[i];
+  __syncthreads();
+  float M = -INFINITY;
+  for (int w = 0; w < 4; ++w) M = fmaxf(M, part[w * (2 + r)]);
+  float f[4], tot = 0.f;
+  for (int w = 0; w < 4; ++w) {
+    const float mw = part[w * (2 + r)];
+    f[w] = mw == -INFINITY ? 0.f : expf(mw - M);
+    tot += f[w] * part[w * (2 + r) + 1];
+  }
+  T* orow = static_cast<T*>(p.ol) + ((int64_t)t * p.a.heads + hd) * r;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) {
+    float v = 0.f;
+    for (int w = 0; w < 4; ++w) v += f[w] * part[w * (2 + r) + 2 + c];
+    orow[c] = cvt<T>(v / tot);
+  }
+}
+
+// --------------------------------------------------------------------------------------------------------------- mLSTM
+// One warp per (sequence, head, state column): lane l holds rows l, l + 32, … of its column of S; column vdim is the
+// normaliser n (the column whose "value" is 1).  Every warp carries its own copy of the running maximum m, so columns
+// never read what another column's warp wrote.  Per token: the capped gates, m_t = max(f + m, i), the column's decay and
+// update, then the column's dot with q (a numerator of the output, or n·q).  The next token's operands are requested
+// while the current one is summed.  Eight columns per CTA.
+constexpr int kRecDR = kMlstmMaxDim / 32;
+__device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int seg = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dk = p.a.dim, dv = p.a.vdim, H = p.a.heads;
+  const int j = blockIdx.z * 8 + warp;
+  if (j > dv) return;
+  const int r0 = p.seg_row0 != nullptr ? p.seg_row0[seg] : seg;
+  const int cnt = p.seg_count != nullptr ? p.seg_count[seg] : 1;
+  const int pos0 = p.pos[r0];
+  float* st = p.state + (int64_t)p.slot[r0] * p.slot_stride + (int64_t)hd * ((int64_t)dk * (dv + 1) + dv + 1);
+  float* st_m = st + (int64_t)dk * (dv + 1);
+  float S[kRecDR], m = 0.f;
+#pragma unroll
+  for (int i = 0; i < kRecDR; ++i) {
+    const int d = lane + 32 * i;
+    S[i] = (pos0 > 0 && d < dk) ? st[(int64_t)d * (dv + 1) + j] : 0.f;
+  }
+  if (pos0 > 0) m = st_m[j];
+  const float qs = rsqrtf((float)dk), cap = p.gate_cap;
+  const T* P = static_cast<const T*>(p.proj);
+  float qn[kRecDR], kn[kRecDR], vn = 1.f, zi = 0.f, zf = 0.f;
+  auto fetch = [&](int row) {
+    const T* pr = P + (int64_t)row * p.ld_proj;
+#pragma unroll
+    for (int i = 0; i < kRecDR; ++i) {
+      const int d = lane + 32 * i;
+      qn[i] = d < dk ? ldf<T>(pr + p.off_q + hd * dk + d) : 0.f;
+      kn[i] = d < dk ? ldf<T>(pr + p.off_k + hd * dk + d) : 0.f;
+    }
+    vn = j < dv ? ldf<T>(pr + p.off_v + hd * dv + j) : 1.f;
+    zi = p.gates[(int64_t)row * p.ld_gates + hd];
+    zf = p.gates[(int64_t)row * p.ld_gates + H + hd];
+  };
+  fetch(r0);
+  for (int t = 0; t < cnt; ++t) {
+    float qc[kRecDR], kc[kRecDR];
+#pragma unroll
+    for (int i = 0; i < kRecDR; ++i) {
+      qc[i] = qn[i] * qs;
+      kc[i] = kn[i];
+    }
+    const float v = vn, gi = cap * tanhf(zi / cap), gf = log_sigmoid(cap * tanhf(zf / cap));
+    if (t + 1 < cnt) fetch(r0 + t + 1);
+    const float m_new = fmaxf(gf + m, gi);
+    const float a = expf(gf + m - m_new), b = expf(gi - m_new) * v;
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRecDR; ++i) {
+      S[i] = fmaf(a, S[i], b * kc[i]);
+      dot = fmaf(S[i], qc[i], dot);
+    }
+    dot = warp_sum(dot);
+    m = m_new;
+    if (lane == 0) {
+      float* orow = p.o + ((int64_t)(r0 + t) * H + hd) * (dv + 2);
+      orow[j] = dot;
+      if (j == dv) orow[dv + 1] = m;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRecDR; ++i) {
+    const int d = lane + 32 * i;
+    if (d < dk) st[(int64_t)d * (dv + 1) + j] = S[i];
+  }
+  if (lane == 0) st_m[j] = m;
+}
+
+// One warp per (token, head): o = numerators / (max(|n·q|, e^(−m)) + 1e-6), o / rms(o), · head_norm · sigmoid(out gate).
+template <typename T>
+__global__ void __launch_bounds__(128) mlstm_out_kernel(const MlstmRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int pair = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  const int H = p.a.heads, dv = p.a.vdim;
+  if (pair >= p.n_tok * H) return;
+  const int t = pair / H, hd = pair % H;
+  const float* orow = p.o + (int64_t)pair * (dv + 2);
+  const float den = fmaxf(fabsf(orow[dv]), expf(-orow[dv + 1])) + 1e-6f;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float v = orow[c] / den;
+    ss += v * v;
+  }
+  const float inv = rsqrtf(warp_sum(ss) / (float)dv + p.eps);
+  const T* g = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj + p.off_g + hd * dv;
+  T* y = static_cast<T*>(p.mid) + (int64_t)t * p.ld_mid + hd * dv;
+  for (int c = lane; c < dv; c += 32) {
+    const float gate = 1.f / (1.f + expf(-ldf<T>(g + c)));
+    y[c] = cvt<T>(orow[c] / den * inv * p.head_norm[hd * dv + c] * gate);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------ routed experts
+// One warp per token: the `top` largest router logits (the sigmoid is monotonic, so the order is that of the scores; ties
+// go to the lower index), their sigmoids as weights, and a count per expert.
+__global__ void __launch_bounds__(128) moe_route_kernel(const MoeRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= p.n_tok) return;
+  const int E = p.m.experts, top = p.m.top;
+  const float* z = p.z + (int64_t)t * E;
+  float last_v = INFINITY;
+  int last_i = -1;
+  for (int k = 0; k < top; ++k) {
+    // the best entry that comes after (last_v, last_i) in the order (value descending, index ascending)
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float v = z[e];
+      const bool after = v < last_v || (v == last_v && e > last_i);
+      if (after && (v > bv || (v == bv && e < bi))) {
+        bv = v;
+        bi = e;
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (bi == 0x7fffffff) bi = 0;   // fewer finite logits than choices: cannot happen with top <= experts
+    if (lane == 0) {
+      p.sel_e[(int64_t)t * top + k] = bi;
+      p.sel_w[(int64_t)t * top + k] = 1.f / (1.f + expf(-bv));
+      atomicAdd(p.plan + bi, 1);
+    }
+    last_v = bv;
+    last_i = bi;
+  }
+}
+
+// One CTA: counts → group ends, the row tiles of every group, and a sorted position for every pair.
+__global__ void __launch_bounds__(256) moe_plan_kernel(const MoeRun p) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ int sh[];   // cursor [E]
+  const int E = p.m.experts, P = p.n_tok * p.m.top, n_tiles = moe_tiles(P, E);
+  int32_t* counts = p.plan;
+  int32_t* group_end = p.plan + E;
+  int32_t* tile_group = p.plan + 2 * E;
+  int32_t* tile_row0 = tile_group + n_tiles;
+  if (threadIdx.x == 0) {
+    int row = 0, tile = 0;
+    for (int e = 0; e < E; ++e) {
+      sh[e] = row;
+      const int end = row + counts[e];
+      for (int r0 = row; r0 < end; r0 += 64) {
+        tile_group[tile] = e;
+        tile_row0[tile] = r0;
+        ++tile;
+      }
+      row = end;
+      group_end[e] = end;
+    }
+    for (; tile < n_tiles; ++tile) tile_group[tile] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < P; i += blockDim.x) p.pair_slot[i] = atomicAdd(&sh[p.sel_e[i]], 1);
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next routing
+}
+
+// a_perm[slot of pair, :] = T(score · h[token, :])
+template <typename T>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const MoeRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int pair = blockIdx.x, t = pair / p.m.top;
+  const float w = p.sel_w[pair];
+  const T* src = static_cast<const T*>(p.h) + (int64_t)t * p.width;
+  T* dst = static_cast<T*>(p.a_perm) + (int64_t)p.pair_slot[pair] * p.width;
+  for (int i = threadIdx.x; i < p.width; i += blockDim.x) dst[i] = cvt<T>(w * ldf<T>(src + i));
+}
+
+// y[t, :] = Σ_k outp[slot of (t, k), :] + sigmoid(sg[t]) · shared[t, :]
+template <typename T>
+__global__ void __launch_bounds__(128) moe_combine_kernel(const MoeRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, top = p.m.top;
+  float gate = 0.f;
+  if (p.shared != nullptr) gate = 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
+  for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) v += p.outp[(int64_t)p.pair_slot[(int64_t)t * top + k] * p.width + i];
+    if (p.shared != nullptr) {
+      const int64_t o = (int64_t)t * p.width + i;
+      v += gate * (p.shared_f32 ? static_cast<const float*>(p.shared)[o] : ldf<T>(static_cast<const T*>(p.shared) + o));
+    }
+    p.y[(int64_t)t * p.width + i] = v;
+  }
+}
+
+}  // namespace
+
+#define MIX_DTYPE_CHECK(dtype) \
+  B200_CHECK_ARG((dtype) == B200_BF16 || (dtype) == B200_F32, "stack op: unknown dtype %d", (int)(dtype))
+
+int launch_stack_norm(void* y, const float* x, const float* w, const int32_t* rows, int64_t n_rows, int dim, float eps,
+                      float offset, int kind, int dtype, cudaStream_t st) {
+  if (kind == B200_NORM_RMS) return launch_stack_rmsnorm(y, x, w, rows, n_rows, dim, eps, offset, dtype, st);
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(kind == B200_NORM_LAYER, "stack norm: unknown kind %d", kind);
+  B200_CHECK_ARG(y && x && w && n_rows > 0 && dim > 0, "stack norm: bad arguments");
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_layernorm_kernel<float, float, false>, dim3((unsigned)n_rows), dim3(256), 0, st, stack_pdl(),
+                         (float*)y, (float*)nullptr, x, w, rows, dim, eps, offset, 1.f));
+  else
+    B200_CUDA(launch_pdl(stack_layernorm_kernel<float, __nv_bfloat16, false>, dim3((unsigned)n_rows), dim3(256), 0, st,
+                         stack_pdl(), (__nv_bfloat16*)y, (float*)nullptr, x, w, rows, dim, eps, offset, 1.f));
+  return B200_OK;
+}
+
+int launch_stack_norm_add(float* x, const void* y, bool y_bf16, const float* w, int64_t rows, int dim, float eps, float mult,
+                          int kind, cudaStream_t st) {
+  if (kind == B200_NORM_RMS)
+    return y_bf16 ? launch_stack_rms_add_bf16(x, (const __nv_bfloat16*)y, w, rows, dim, eps, mult, st)
+                  : launch_stack_rms_add(x, (const float*)y, w, rows, dim, eps, mult, st);
+  B200_CHECK_ARG(kind == B200_NORM_LAYER, "stack norm_add: unknown kind %d", kind);
+  B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack norm_add: bad arguments");
+  if (y_bf16)
+    B200_CUDA(launch_pdl(stack_layernorm_kernel<__nv_bfloat16, float, true>, dim3((unsigned)rows), dim3(256), 0, st,
+                         stack_pdl(), (float*)nullptr, x, (const __nv_bfloat16*)y, w, (const int32_t*)nullptr, dim, eps, 0.f,
+                         mult));
+  else
+    B200_CUDA(launch_pdl(stack_layernorm_kernel<float, float, true>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(),
+                         (float*)nullptr, x, (const float*)y, w, (const int32_t*)nullptr, dim, eps, 0.f, mult));
+  return B200_OK;
+}
+
+int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu, int64_t rows, int n, float limit, int dtype,
+                           cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(y && gu && rows > 0 && n > 0, "stack glu_clamp: bad arguments");
+  const int64_t total = rows * n;
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_glu_clamp_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), (float*)y,
+                         ld_y, (const float*)gu, ld_gu, n, limit, total));
+  else
+    B200_CUDA(launch_pdl(stack_glu_clamp_kernel<__nv_bfloat16>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(),
+                         (__nv_bfloat16*)y, ld_y, (const __nv_bfloat16*)gu, ld_gu, n, limit, total));
+  return B200_OK;
+}
+
+int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total, float cap, cudaStream_t st) {
+  B200_CHECK_ARG(logits && total > 0 && cap > 0.f, "stack softcap: bad arguments");
+  // copies and the argmax follow: a full dependency
+  B200_CUDA(launch_pdl(stack_softcap_kernel, dim3(grid_cap(total, 256)), dim3(256), 0, st, false, logits, logits_bf, total, cap));
+  return B200_OK;
+}
+
+int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  const int r = p.l.kv_rank, dr = p.l.rot_dim, H = p.a.heads, dn = p.a.dim, kd = r + dr;
+  B200_CHECK_ARG(p.proj && p.cache && p.slot && p.pos && p.qa && p.ol && p.out && p.n_tok > 0, "latent attention: null argument");
+  B200_CHECK_ARG(H > 0 && dn > 0 && p.a.vdim > 0 && r > 0 && dr >= 0 && p.l.rot_dims >= 0 && p.l.rot_dims <= dr &&
+                     p.l.rot_dims % 2 == 0,
+                 "latent attention: bad sizes");
+  B200_CHECK_ARG(r <= kLatentMaxRank, "latent attention: kv_rank above %d not built", kLatentMaxRank);
+  B200_CHECK_ARG(p.l.c_norm && p.l.uk_t && p.l.uv && (p.l.rot_dims == 0 || p.l.rot_table), "latent attention: null weight");
+  int rc;
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(latent_prep_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  const size_t esz = dtype == B200_F32 ? 4 : 2;
+  StackGemm g;   // folded query of head h = uk_hᵀ · q_plain of head h
+  g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.k1 = dn; g.sa = dn + dr;
+  g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
+  g.M = p.n_tok; g.N = r; g.K = dn; g.batch = H;
+  g.epi = SEPI_STORE; g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;
+  if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
+  const size_t smem = (size_t)(kd + 4 * (2 + r)) * 4;
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
+  StackGemm v;   // head h's output = uv_h · (softmax-weighted latent of head h)
+  v.a = p.ol; v.lda = (int64_t)H * r; v.k1 = r; v.sa = r;
+  v.w = p.l.uv; v.sw = (int64_t)p.a.vdim * r;
+  v.M = p.n_tok; v.N = p.a.vdim; v.K = r; v.batch = H;
+  v.epi = SEPI_STORE; v.c = p.out; v.ldc = p.ld_out; v.sc = p.a.vdim;
+  return launch_stack_gemm(v, dtype, st);
+}
+
+int run_mlstm(const MlstmRun& p, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(p.proj && p.gates && p.state && p.slot && p.pos && p.o && p.n_seg > 0 && p.n_tok > 0, "mlstm: null argument");
+  B200_CHECK_ARG(p.a.heads > 0 && p.a.dim > 0 && p.a.vdim > 0 && p.gate_cap > 0.f, "mlstm: bad sizes");
+  B200_CHECK_ARG(p.a.dim <= kMlstmMaxDim, "mlstm: key size above %d not built", kMlstmMaxDim);
+  const dim3 grid(p.n_seg, p.a.heads, (p.a.vdim + 1 + 7) / 8);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(mlstm_scan_kernel<float>, grid, dim3(256), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(mlstm_scan_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, stack_pdl(), p));
+  if (p.mid == nullptr) return B200_OK;
+  B200_CHECK_ARG(p.head_norm != nullptr, "mlstm: null head norm");
+  const dim3 og((p.n_tok * p.a.heads + 3) / 4);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(mlstm_out_kernel<float>, og, dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(mlstm_out_kernel<__nv_bfloat16>, og, dim3(128), 0, st, stack_pdl(), p));
+  return B200_OK;
+}
+
+int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  const b200_moe_desc& m = p.m;
+  B200_CHECK_ARG(p.h && p.z && p.sel_e && p.sel_w && p.plan && p.pair_slot && p.a_perm && p.gu && p.act && p.outp && p.y &&
+                     p.n_tok > 0 && p.width > 0,
+                 "moe: null argument");
+  B200_CHECK_ARG(m.experts > 0 && m.top > 0 && m.top <= m.experts && m.expert_ff > 0 && m.router && m.w_exp_in && m.w_exp_out,
+                 "moe: bad description");
+  B200_CHECK_ARG(m.experts <= 8192, "moe: more than 8192 experts not built");
+  const int P = p.n_tok * m.top, n_tiles = moe_tiles(P, m.experts), E = m.experts;
+  int rc;
+  StackGemm rz;   // router logits in fp32
+  rz.a = p.h; rz.lda = p.width; rz.k1 = p.width;
+  rz.w = m.router; rz.M = p.n_tok; rz.N = E; rz.K = p.width;
+  rz.epi = SEPI_STORE_F32; rz.c = p.z; rz.ldc = E;
+  if ((rc = launch_stack_gemm(rz, dtype, st)) != B200_OK) return rc;
+  B200_CUDA(launch_pdl(moe_route_kernel, dim3((p.n_tok + 3) / 4), dim3(128), 0, st, stack_pdl(), p));
+  B200_CUDA(launch_pdl(moe_plan_kernel, dim3(1), dim3(256), (size_t)E * 4, st, stack_pdl(), p));
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+  StackGemm g;
+  g.a = p.a_perm; g.lda = p.width; g.k1 = p.width;
+  g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width;
+  g.M = P; g.N = 2 * m.expert_ff; g.K = p.width;
+  g.epi = SEPI_STORE; g.c = p.gu; g.ldc = 2 * m.expert_ff;
+  g.tile_group = p.plan + 2 * E; g.tile_row0 = p.plan + 2 * E + n_tiles; g.group_end = p.plan + E; g.n_tiles = n_tiles;
+  if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
+  if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, 2 * m.expert_ff, P, m.expert_ff, m.limit, dtype, st)) != B200_OK)
+    return rc;
+  StackGemm d;
+  d.a = p.act; d.lda = m.expert_ff; d.k1 = m.expert_ff;
+  d.w = m.w_exp_out; d.sw = (int64_t)p.width * m.expert_ff;
+  d.M = P; d.N = p.width; d.K = m.expert_ff;
+  d.epi = SEPI_STORE_F32; d.c = p.outp; d.ldc = p.width;
+  d.tile_group = g.tile_group; d.tile_row0 = g.tile_row0; d.group_end = g.group_end; d.n_tiles = n_tiles;
+  if ((rc = launch_stack_gemm(d, dtype, st)) != B200_OK) return rc;
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  return B200_OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,97 @@
+// stack_mix.cuh — mixers and feed-forwards of sandwich blocks (stack_mix.cu): layer norm, latent attention, the mLSTM
+// matrix memory, routed experts, soft-capped logits.  Storage type T = bf16 or fp32; fp32 arithmetic for norms, softmax,
+// routing, gates, the recurrence and its state.
+#pragma once
+#include "stack.cuh"
+
+namespace b200 {
+
+// y[r, :] = T(norm(x[rows ? rows[r] : r, :]) · (offset + w)), norm of b200_norm_kind `kind`
+int launch_stack_norm(void* y, const float* x, const float* w, const int32_t* rows_or_null, int64_t n_rows, int dim,
+                      float eps, float offset, int kind, int dtype, cudaStream_t st);
+// x[r, :] += mult · norm(y[r, :]) · w, y fp32 or bf16
+int launch_stack_norm_add(float* x, const void* y, bool y_bf16, const float* w, int64_t rows, int dim, float eps, float mult,
+                          int kind, cudaStream_t st);
+// y[r, j] = T(min(g, limit)·sigmoid(1.702·min(g, limit))·(clamp(u, ±limit) + 1)), g = gu[r, j], u = gu[r, n + j]
+int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu, int64_t rows, int n, float limit, int dtype,
+                           cudaStream_t st);
+// logits (fp32) and their bf16 copy <- cap·tanh(logits / cap)
+int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total, float cap, cudaStream_t st);
+
+// ---- latent attention: everything between the in-projection and the out-projection
+constexpr int kLatentMaxRank = 512;
+struct LatentRun {
+  b200_attn_desc a{};
+  b200_latent_desc l{};
+  float eps = 1e-5f;
+  const void* proj = nullptr;    // [n_tok, ld_proj] T: q at off_q (heads·(dim + rot_dim)), down at off_down (kv_rank + rot_dim)
+  int64_t ld_proj = 0;
+  int off_q = 0, off_down = 0;
+  void* cache = nullptr;         // this run's rows of slot 0: [max_ctx][kv_rank + rot_dim] T; slot s is s·slot_stride further
+  int64_t slot_stride = 0;
+  const int32_t* slot = nullptr;
+  const int32_t* pos = nullptr;
+  int n_tok = 0;
+  void* qa = nullptr;            // [n_tok, heads·(kv_rank + rot_dim)] T: the query folded through uk, and its rotated part
+  void* ol = nullptr;            // [n_tok, heads·kv_rank] T: softmax-weighted latents
+  void* out = nullptr;           // [n_tok, ld_out] T: head h at columns h·vdim
+  int64_t ld_out = 0;
+  // decode-shaped steps (few rows, long key lists): keys split over CTAs, partial softmaxes merged by the CTA that
+  // finishes last (ticket)
+  float* split_ws = nullptr;
+  unsigned int* split_tickets = nullptr;
+  int nsplit = 1, keys_per_split = 0;
+};
+int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st);
+
+// ---- mLSTM: recurrence + head norm + output gate
+constexpr int kMlstmMaxDim = 512;
+struct MlstmRun {
+  b200_attn_desc a{};            // heads, dim (key size), vdim
+  float gate_cap = 15.f, eps = 1e-5f;
+  const void* proj = nullptr;    // [n_tok, ld_proj] T: q | k | v | out-gate logits at off_q / off_k / off_v / off_g
+  int64_t ld_proj = 0;
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0;
+  const float* gates = nullptr;  // [n_tok, ld_gates]: 2·heads raw input- and forget-gate logits per row
+  int64_t ld_gates = 0;
+  float* state = nullptr;        // this run's state of slot 0; slot s is s·slot_stride floats further
+  int64_t slot_stride = 0;
+  const int32_t* seg_row0 = nullptr;   // [n_seg] first row / row count of every sequence; null: every row is a sequence
+  const int32_t* seg_count = nullptr;
+  const int32_t* slot = nullptr;       // per row
+  const int32_t* pos = nullptr;        // per row
+  int n_seg = 0, n_tok = 0;
+  float* o = nullptr;            // [n_tok, heads·(vdim + 2)] fp32: numerators | n·q | m
+  const float* head_norm = nullptr;
+  void* mid = nullptr;           // [n_tok, ld_mid] T: normed, gated head outputs
+  int64_t ld_mid = 0;
+};
+// floats of state per head: S [dim][vdim + 1] (column vdim is the normaliser n) and the running maximum per column
+inline int64_t mlstm_state_floats(int heads, int dim, int vdim) { return (int64_t)heads * ((int64_t)dim * (vdim + 1) + vdim + 1); }
+int run_mlstm(const MlstmRun& p, int dtype, cudaStream_t st);
+
+// ---- routed experts
+struct MoeRun {
+  b200_moe_desc m{};
+  int width = 0, n_tok = 0;
+  const void* h = nullptr;       // [n_tok, width] T
+  float* z = nullptr;            // [n_tok, experts] router logits
+  int32_t* sel_e = nullptr;      // [n_tok·top] chosen expert of every (token, choice) pair
+  float* sel_w = nullptr;        // [n_tok·top] its score
+  int32_t* plan = nullptr;       // counts [E] | group_end [E] | tile_group [n_tiles] | tile_row0 [n_tiles]
+  int32_t* pair_slot = nullptr;  // [n_tok·top] sorted position of a pair
+  void* a_perm = nullptr;        // [P, width] T: score·h of every pair, sorted by expert
+  void* gu = nullptr;            // [P, 2·expert_ff] T
+  void* act = nullptr;           // [P, expert_ff] T
+  float* outp = nullptr;         // [P, width] fp32
+  float* y = nullptr;            // [n_tok, width] fp32 result
+  const void* shared = nullptr;  // [n_tok, width] T or fp32 (shared_f32): shared expert's output, or null
+  bool shared_f32 = false;
+  const void* sg = nullptr;      // T: the shared gate's logit of token t at sg[t·ld_sg]
+  int64_t ld_sg = 0;
+};
+__host__ __device__ inline int moe_tiles(int pairs, int experts) { return (pairs + 63) / 64 + experts; }
+inline int64_t moe_plan_ints(int pairs, int experts) { return 2 * (int64_t)experts + 2 * moe_tiles(pairs, experts); }
+int run_moe(const MoeRun& p, int dtype, cudaStream_t st);
+
+}  // namespace b200

@@ -55,23 +55,38 @@ __global__ void __launch_bounds__(256) stack_gemm_kernel(const StackGemm g) {
   pdl_wait();
   __shared__ float As[kBK][kBM + 4];
   __shared__ float Ws[kBK][kBN + 4];
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * kBN;
+  // which rows and which operands this CTA serves: a plain tile, a tile of batch item blockIdx.z (operands moved by
+  // sa / sw / sc elements per item), or tile blockIdx.y of a grouped product (rows of group e meet matrix e)
+  int m0 = blockIdx.y * kBM, m_end = g.M;
+  int64_t za = 0, zw = 0, zc = 0;
+  if (g.tile_group != nullptr) {
+    const int e = g.tile_group[blockIdx.y];
+    if (e < 0) return;
+    m0 = g.tile_row0[blockIdx.y];
+    m_end = min(m0 + kBM, g.group_end[e]);
+    zw = (int64_t)e * g.sw;
+  } else {
+    za = (int64_t)blockIdx.z * g.sa;
+    zw = (int64_t)blockIdx.z * g.sw;
+    zc = (int64_t)blockIdx.z * g.sc;
+  }
+  const int n0 = blockIdx.x * kBN;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  const T* W = static_cast<const T*>(g.w);
+  const T* W = static_cast<const T*>(g.w) + zw;
   for (int k0 = 0; k0 < g.K; k0 += kBK) {
     for (int e = threadIdx.x; e < kBM * kBK; e += 256) {
       const int r = e / kBK, c = e % kBK;
       const int m = m0 + r, k = k0 + c;
       float v = 0.f;
-      if (m < g.M && k < g.K) {
+      if (m < m_end && k < g.K) {
         const bool first = k < g.k1;
         const void* src = first ? g.a : g.a2;
-        const int64_t idx = first ? (int64_t)m * g.lda + k : (int64_t)m * g.lda2 + (k - g.k1);
+        const int64_t idx = first ? (int64_t)m * g.lda + k + za : (int64_t)m * g.lda2 + (k - g.k1);
         v = g.a_f32 ? as_operand<T>(static_cast<const float*>(src)[idx]) : ldf<T>(static_cast<const T*>(src) + idx);
       }
       As[c][r] = v;
@@ -96,14 +111,14 @@ __global__ void __launch_bounds__(256) stack_gemm_kernel(const StackGemm g) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int m = m0 + ty * 4 + i;
-    if (m >= g.M) continue;
+    if (m >= m_end) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
       if (n >= g.N) continue;
       float v = acc[i][j];
       if (g.bias != nullptr) v += g.bias[n];
-      const int64_t o = (int64_t)m * g.ldc + n;
+      const int64_t o = (int64_t)m * g.ldc + n + zc;
       switch (g.epi) {
         case SEPI_STORE: static_cast<T*>(g.c)[o] = cvt<T>(v); break;
         case SEPI_STORE_F32: static_cast<float*>(g.c)[o] = v; break;
@@ -114,6 +129,7 @@ __global__ void __launch_bounds__(256) stack_gemm_kernel(const StackGemm g) {
           break;
         }
         default:
+          if (g.softcap > 0.f) v = g.softcap * tanhf(v / g.softcap);
           static_cast<float*>(g.c)[o] = v;
           if (g.c2 != nullptr) g.c2[o] = __float2bfloat16_rn(v);
       }
@@ -213,10 +229,15 @@ __global__ void __launch_bounds__(256) stack_act_mul_kernel(T* __restrict__ y, i
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = e / n;
     const int j = (int)(e % n);
-    const float gv = ldf<T>(g + r * ld_gu + j), uv = ldf<T>(u + r * ld_gu + j);
+    const float gv = ldf<T>(g + r * ld_gu + j);
+    const float av = act == B200_ACT_SILU ? silu(gv)
+                     : act == B200_ACT_GELU_ERF ? 0.5f * gv * (1.f + erff(gv * 0.70710678118654752f)) : gelu_tanh(gv);
+    if (u == nullptr) {   // the activation alone
+      y[r * ld_y + j] = cvt<T>(av);
+      continue;
+    }
     // the activation is a value of type T before it meets the other factor
-    const float a = as_operand<T>(act == B200_ACT_SILU ? silu(gv) : gelu_tanh(gv));
-    y[r * ld_y + j] = cvt<T>(a * uv);
+    y[r * ld_y + j] = cvt<T>(as_operand<T>(av) * ldf<T>(u + r * ld_gu + j));
   }
 }
 
@@ -675,7 +696,10 @@ int launch_stack_gemm(const StackGemm& g, int dtype, cudaStream_t st) {
                  g.K);
   B200_CHECK_ARG(g.k1 == g.K || g.a2 != nullptr, "stack gemm: second operand source missing");
   B200_CHECK_ARG(g.epi != SEPI_ACT_TABLE || (g.table && g.tok), "stack gemm: table epilogue without a table");
-  const dim3 grid((g.N + kBN - 1) / kBN, (g.M + kBM - 1) / kBM);
+  B200_CHECK_ARG(g.batch >= 1 && (g.batch == 1 || g.a2 == nullptr), "stack gemm: bad batch");
+  B200_CHECK_ARG(g.tile_group == nullptr || (g.tile_row0 && g.group_end && g.n_tiles > 0 && g.batch == 1),
+                 "stack gemm: incomplete grouping");
+  const dim3 grid((g.N + kBN - 1) / kBN, g.tile_group ? g.n_tiles : (g.M + kBM - 1) / kBM, g.batch);
   if (dtype == B200_F32) B200_CUDA(launch_pdl(stack_gemm_kernel<float>, grid, dim3(256), 0, st, stack_pdl(), g));
   else B200_CUDA(launch_pdl(stack_gemm_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, stack_pdl(), g));
   return B200_OK;
@@ -732,8 +756,9 @@ int launch_stack_act_table(__nv_bfloat16* y, const __nv_bfloat16* g, const void*
 int launch_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, int64_t ld_gu, int64_t rows, int n, int act,
                          int dtype, cudaStream_t st) {
   STACK_DTYPE_CHECK(dtype);
-  B200_CHECK_ARG(y && g && u && rows > 0 && n > 0, "stack act_mul: bad arguments");
-  B200_CHECK_ARG(act == B200_ACT_GELU_TANH || act == B200_ACT_SILU, "stack act_mul: unknown activation %d", act);
+  B200_CHECK_ARG(y && g && rows > 0 && n > 0, "stack act_mul: bad arguments");
+  B200_CHECK_ARG(act == B200_ACT_GELU_TANH || act == B200_ACT_SILU || act == B200_ACT_GELU_ERF,
+                 "stack act_mul: unknown activation %d", act);
   const int64_t total = rows * n;
   if (dtype == B200_F32)
     B200_CUDA(launch_pdl(stack_act_mul_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), (float*)y, ld_y,

@@ -17,8 +17,8 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import models
-from ._lib import (AttnDesc, B200Error, LayerWeights, ModelDesc, StackDesc, StackLayer, WeightTable, check, lib,
-                   require_device)
+from ._lib import (AttnDesc, B200Error, LatentDesc, LayerWeights, MlstmDesc, ModelDesc, MoeDesc, StackDesc, StackLayer,
+                   WeightTable, check, lib, require_device)
 
 
 def align_prompts(token_lists, context_size: int, pad_token: int):
@@ -152,9 +152,13 @@ class DecodeEngine:
                 raise B200Error(f"DecodeEngine: {name} must be a contiguous {dt} tensor on {dev}")
             return t.data_ptr()
 
-        acts = {"gelu_tanh": 0, "silu": 1}
+        acts = {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}
         arr = (StackLayer * len(spec.layers))()
-        for i, L in enumerate(spec.layers):
+        sandwich = spec.block == "sandwich"
+        self._rot_tables = {}
+        for i, L in enumerate(spec.layers if sandwich else ()):
+            arr[i] = self._sandwich_layer(spec, i, L, ptr, mdt, acts)
+        for i, L in enumerate(() if sandwich else spec.layers):
             a, lay, p = L.attn, spec.layout(i), f"l{i}."
             side = spec.side_dim > 0
             arr[i] = StackLayer(AttnDesc(a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window, a.keep_first,
@@ -168,16 +172,47 @@ class DecodeEngine:
         runs = spec.runs()
         run_layer = (C.c_int32 * len(runs))(*[r[0] for r in runs])
         run_mix = (C.c_int32 * len(runs))(*[int(r[1]) for r in runs])
-        desc = StackDesc(1 if mdt == torch.float32 else 0, 0, spec.width, spec.vocab, len(spec.layers), len(runs),
+        desc = StackDesc(1 if mdt == torch.float32 else 0, int(sandwich), spec.width, spec.vocab, len(spec.layers), len(runs),
                          run_layer, run_mix, spec.embed_scale, spec.residual_mult, spec.norm_eps, spec.norm_offset,
                          spec.side_dim, spec.side_dim * len(spec.layers), spec.max_ctx, spec.max_slots,
                          ptr("embed", mdt), ptr("mix_in", mdt), ptr("side_table", mdt), ptr("final_norm", torch.float32),
-                         ptr("head", mdt), arr)
+                         ptr("head", mdt), arr, {"rms": 0, "layer": 1}[spec.norm_kind], spec.logit_softcap)
         h = C.c_void_p()
         with torch.cuda.device(dev):
             check(lib().b200_engine_create_stack(C.byref(desc), C.byref(h)), "b200_engine_create_stack")
         self._h = h
         self.slots = SequenceSlots(spec.max_slots)
+
+    def _sandwich_layer(self, spec, i, L, ptr, mdt, acts) -> StackLayer:
+        """Descriptor of layer i of a sandwich-block model (latent attention or mLSTM mixer; dense or routed
+        feed-forward); the rotation tables are built here, for the engine's context length."""
+        lay, p = spec.mix_layout(i), f"l{i}."
+        f32 = torch.float32
+        lat, rec, moe = LatentDesc(), MlstmDesc(), MoeDesc()
+        if L.mixer == "latent_attention":
+            a = L.latent
+            attn = AttnDesc(a.heads, 1, a.dim, a.vdim, a.scale, 0, 0, 0)
+            tab = self._rot_tables.get(a.rot)
+            if tab is None and a.rot.dims > 0:
+                tab = self._rot_tables[a.rot] = a.rot.table(spec.max_ctx).contiguous().to(self.device)
+            lat = LatentDesc(a.kv_rank, a.rot_dim, a.rot.dims, ptr(p + "c_norm", f32), ptr(p + "uk_t", mdt), ptr(p + "uv", mdt),
+                             tab.data_ptr() if tab is not None else None)
+            mixer = 1
+        else:
+            a = L.mlstm
+            attn = AttnDesc(a.heads, a.heads, a.dim, a.vdim, 1.0, 0, 0, 0)
+            rec = MlstmDesc(a.gate_cap, ptr(p + "head_norm", f32))
+            mixer = 2
+        has_ff = L.ff_kind == "moe" or L.ff > 0
+        if L.ff_kind == "moe":
+            m = L.moe
+            moe = MoeDesc(m.experts, m.top, m.expert_ff, m.shared_ff, m.limit, m.shared_limit, ptr(p + "router", mdt),
+                          ptr(p + "w_exp_in", mdt), ptr(p + "w_exp_out", mdt))
+        return StackLayer(attn, L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate, 0, lay.n_in,
+                          0, lay.k_out, ptr(p + "norm", f32), ptr(p + "w_in", mdt), ptr(p + "b_in", f32), ptr(p + "w_out", mdt),
+                          0, None, None, None, mixer, 2 if L.ff_kind == "moe" else 1, ptr(p + "post_norm", f32),
+                          ptr(p + "ff_norm", f32) if has_ff else None, ptr(p + "ff_post_norm", f32) if has_ff else None,
+                          ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), lat, rec, moe)
 
     # --------------------------------------------------------------------------------- ragged steps (stack engines)
     def step(self, entries, greedy: bool = False) -> torch.Tensor:

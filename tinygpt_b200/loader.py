@@ -366,7 +366,7 @@ def load_stack_checkpoint(model_dir: str | Path, device: str | torch.device = "c
     spec = load_stack_config(model_dir, max_ctx, max_slots)
     f = SafeTensorsFile(Path(model_dir) / "model.safetensors")
     named: Dict[str, torch.Tensor] = {}
-    for name, shape in models.kozusun_tensor_shapes(spec).items():
+    for name, shape in models.ARCHITECTURES[spec.architecture].tensor_shapes(spec).items():
         info = f.header.get(name)
         if info is None:
             raise LoaderError(f"missing tensor: {name}")
@@ -382,7 +382,7 @@ def load_stack_checkpoint(model_dir: str | Path, device: str | torch.device = "c
         a = np.frombuffer(f._mm, dtype=np_dt, count=n, offset=f._base + start).reshape(shape).copy()
         t = torch.from_numpy(a)
         named[name] = t.view(torch.bfloat16) if t_dt == torch.bfloat16 else t
-    w = models.pack_stack_weights(spec, named, device=device, dtype=dtype)
+    w = models.pack_weights(spec, named, device=device, dtype=dtype)
     del named
     f.close()
     return spec, w

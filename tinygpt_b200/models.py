@@ -8,6 +8,7 @@ synthetic tensors of the real shapes.
 from __future__ import annotations
 
 import json
+import math
 import struct
 from dataclasses import dataclass, replace
 from pathlib import Path
@@ -200,10 +201,98 @@ class AttnSpec:
 
 
 @dataclass(frozen=True)
+class RotarySpec:
+    """Rotary positions on the first `dims` entries of a vector, pair (2i, 2i+1) turned by p·f_i at position p
+    (interleaved layout), f_i = base^(-2i/dims).  factor > 0: YaRN stretching — pairs that turn fewer than `slow` times
+    over `original` positions have their frequency divided by `factor`, pairs that turn more than `fast` times keep it,
+    a linear ramp over the pair index in between; cos and sin are scaled by 0.1·ln(factor) + 1."""
+    dims: int
+    base: float
+    factor: float = 0.0
+    original: int = 0
+    fast: float = 0.0
+    slow: float = 0.0
+
+    def frequencies(self) -> Tuple[np.ndarray, float]:
+        """→ (angular frequency per pair [dims/2] in float64, magnitude of cos / sin)."""
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        f = np.power(float(self.base), -2.0 * i / self.dims)
+        if self.factor <= 0:
+            return f, 1.0
+
+        def pair_of(turns: float) -> float:   # the (fractional) pair index that makes `turns` turns over `original` positions
+            return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+
+        lo = max(math.floor(pair_of(self.fast)), 0)
+        hi = min(math.ceil(pair_of(self.slow)), self.dims - 1)
+        ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp), 0.1 * math.log(self.factor) + 1.0
+
+    def table(self, max_ctx: int) -> torch.Tensor:
+        """fp32 [max_ctx, dims/2, 2]: {cos, sin}(p·f_i)·magnitude, angles taken in float64."""
+        f, mag = self.frequencies()
+        ang = np.arange(max_ctx, dtype=np.float64)[:, None] * f[None, :]
+        return torch.from_numpy(np.stack([np.cos(ang) * mag, np.sin(ang) * mag], axis=-1).astype(np.float32))
+
+
+@dataclass(frozen=True)
+class LatentSpec:
+    """Latent attention: per head `dim` plain + `rot_dim` rotated query/key entries and `vdim` value entries; keys and
+    values are expanded from a cached latent of `kv_rank` entries, one rotated key part is shared by all heads."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    rot: RotarySpec
+
+
+@dataclass(frozen=True)
+class MlstmSpec:
+    """mLSTM matrix memory: per head keys / queries of `dim`, values of `vdim`; gate logits capped at ±gate_cap."""
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+
+@dataclass(frozen=True)
+class MoeSpec:
+    """Sigmoid-routed experts: `top` of `experts` per token, the score multiplies the expert's input; clamped gated experts
+    of width expert_ff (clamp `limit`); shared_ff > 0: a shared expert of that width (clamp shared_limit) behind a
+    per-token sigmoid gate."""
+    experts: int
+    top: int
+    expert_ff: int
+    limit: float
+    shared_ff: int = 0
+    shared_limit: float = 0.0
+
+
+@dataclass(frozen=True)
 class StackLayerSpec:
-    attn: AttnSpec
-    ff: int = 0                      # feed-forward width, 0 = none
-    ff_act: str = "gelu_tanh"        # gelu_tanh | silu
+    attn: Optional[AttnSpec] = None  # mixer "attention"
+    ff: int = 0                      # feed-forward width (gated / dense), 0 = none
+    ff_act: str = "gelu_tanh"        # gelu_tanh | silu | gelu_erf
+    mixer: str = "attention"         # attention | latent_attention | mlstm
+    latent: Optional[LatentSpec] = None
+    mlstm: Optional[MlstmSpec] = None
+    ff_kind: str = "gated"           # gated | dense | moe
+    moe: Optional[MoeSpec] = None
+
+
+@dataclass(frozen=True)
+class MixLayout:
+    """Rows of the merged in-projection of a sandwich block's mixer (segments on multiples of 8, zero padding).
+    latent attention: [q | down];  mLSTM: [q | k | v | out-gate logits | input-gate, forget-gate logits]."""
+    off_q: int = 0
+    off_k: int = 0
+    off_v: int = 0
+    off_g: int = 0
+    off_gate: int = 0
+    n_in: int = 0
+    k_out: int = 0
 
 
 @dataclass(frozen=True)
@@ -242,6 +331,10 @@ class StackSpec:
     side_dim: int = 0                # columns of the per-layer token table, 0 = none
     max_ctx: int = 4096              # cache rows per slot
     max_slots: int = 8               # sequences the engine holds at a time
+    block: str = "parallel"          # parallel: x += m·(mixer(h) + ff(h)), one norm | sandwich: a norm before and after
+    norm_kind: str = "rms"           # each sublayer.  rms | layer (weight-only layer norm)
+    loop_mix: bool = True            # every pass of the loop starts with x <- mix_in·[x; x0]
+    logit_softcap: float = 0.0       # > 0: logits <- cap·tanh(logits / cap)
 
     def runs(self) -> List[Tuple[int, bool]]:
         """(layer, mix the embedding in first) for every layer run, in execution order."""
@@ -250,7 +343,7 @@ class StackSpec:
             return [(i, False) for i in range(n)]
         out = [(i, False) for i in range(self.loop_start)]
         for _ in range(self.loop_times):
-            out += [(i, i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
+            out += [(i, self.loop_mix and i == self.loop_start) for i in range(self.loop_start, self.loop_stop)]
         return out + [(i, False) for i in range(self.loop_stop, n)]
 
     def layout(self, i: int) -> StackLayout:
@@ -265,6 +358,21 @@ class StackSpec:
         off_act = _up8(a.heads * a.vdim)
         return StackLayout(off_q, off_k, off_v, off_g, off_gate, off_up, n_in, off_act, off_act + _up8(L.ff))
 
+    def mix_layout(self, i: int) -> MixLayout:
+        L = self.layers[i]
+        if L.mixer == "latent_attention":
+            a = L.latent
+            off_k = _up8(a.heads * (a.dim + a.rot_dim))
+            return MixLayout(off_q=0, off_k=off_k, n_in=off_k + _up8(a.kv_rank + a.rot_dim), k_out=a.heads * a.vdim)
+        if L.mixer == "mlstm":
+            a = L.mlstm
+            off_k = _up8(a.heads * a.dim)
+            off_v = off_k + _up8(a.heads * a.dim)
+            off_g = off_v + _up8(a.heads * a.vdim)
+            off_gate = off_g + _up8(a.heads * a.vdim)
+            return MixLayout(0, off_k, off_v, off_g, off_gate, off_gate + _up8(2 * a.heads), a.heads * a.vdim)
+        raise ValueError(f"mix_layout: layer {i} has mixer {L.mixer!r}")
+
     def with_ctx(self, max_ctx: int, max_slots: Optional[int] = None) -> "StackSpec":
         return replace(self, max_ctx=int(max_ctx), max_slots=int(max_slots if max_slots is not None else self.max_slots))
 
@@ -273,6 +381,19 @@ class StackSpec:
         n = self.vocab * self.width
         for i, mix in self.runs():
             L, a = self.layers[i], self.layers[i].attn
+            if L.mixer == "latent_attention":
+                q = L.latent
+                n += self.width * (q.heads * (q.dim + q.rot_dim) + q.kv_rank + q.rot_dim + q.heads * q.vdim)
+                n += q.heads * (q.dim + q.vdim) * q.kv_rank
+            elif L.mixer == "mlstm":
+                q = L.mlstm
+                n += self.width * (2 * q.heads * q.dim + 3 * q.heads * q.vdim + 2 * q.heads)
+            if L.mixer != "attention":
+                if L.ff_kind == "dense":
+                    n += 2 * L.ff * self.width
+                elif L.ff_kind == "moe":   # the router, the chosen experts, the shared expert and its gate
+                    n += self.width * (L.moe.experts + 3 * L.moe.top * L.moe.expert_ff + 3 * L.moe.shared_ff + 1)
+                continue
             n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.heads if a.out_gate else 0) + 2 * L.ff)
             n += self.width * (a.heads * a.vdim + L.ff) + 2 * self.side_dim * self.width
             n += 2 * self.width * self.width if mix else 0
@@ -309,8 +430,224 @@ def kozusun_from_config(doc: dict, name: str = "Kozusun") -> StackSpec:
     return spec
 
 
-# config.json "architecture" → reader.  (The Llama-family checkpoints are told apart by "model_type": loader.py.)
-ARCHITECTURES: Dict[str, Callable[[dict], StackSpec]] = {"Kozusun": kozusun_from_config}
+# ---------------------------------------------------------------------------------------------------------- Silatar
+def _rotary_from_config(rot: dict) -> RotarySpec:
+    sc = rot.get("scaling") or {}
+    return RotarySpec(dims=int(rot["dims"]), base=float(rot["base"]), factor=float(sc.get("factor", 0.0)),
+                      original=int(sc.get("original", 0)), fast=float(sc.get("fast", 0.0)), slow=float(sc.get("slow", 0.0)))
+
+
+def silatar_from_config(doc: dict, name: str = "Silatar") -> StackSpec:
+    """config.json of the Silatar design → StackSpec.  Silatar: sandwich blocks with weight-only layer norms; mixers are a
+    latent attention (YaRN-stretched interleaved rotary part) or an mLSTM matrix memory; feed-forwards are a dense
+    erf-GELU layer or sigmoid-routed clamped experts with a gated shared expert; a looped span of layers (own cache or
+    state per pass, nothing between passes); tanh-capped logits."""
+    layers = []
+    for i, lc in enumerate(doc["layers"]):
+        kind, m = lc.get("type"), lc["mixer"]
+        kw = {}
+        if kind == "latent_attention":
+            rot = _rotary_from_config(m["rot"])
+            if rot.dims % 2 or rot.dims > int(m["rot_dim"]):
+                raise ValueError(f"Silatar: layer {i}: rot.dims {rot.dims} must be even and at most rot_dim")
+            kw = dict(mixer=kind, latent=LatentSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]),
+                                                    vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]), scale=float(m["scale"]),
+                                                    rot=rot))
+        elif kind == "mlstm":
+            kw = dict(mixer=kind, mlstm=MlstmSpec(heads=int(m["heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                                  gate_cap=float(m["gate_cap"])))
+        else:
+            raise ValueError(f"Silatar: layer {i}: mixer type {kind!r} is not part of the design")
+        mlp = lc.get("mlp")
+        if mlp is None:
+            kw.update(ff_kind="dense", ff=0, ff_act="gelu_erf")
+        elif mlp.get("kind") == "dense":
+            kw.update(ff_kind="dense", ff=int(mlp["ff"]), ff_act="gelu_erf")
+        elif mlp.get("kind") == "moe":
+            sh = mlp.get("shared") or {}
+            kw.update(ff_kind="moe", moe=MoeSpec(experts=int(mlp["router"]["experts"]), top=int(mlp["router"]["top"]),
+                                                 expert_ff=int(mlp["expert"]["ff"]), limit=float(mlp["expert"]["limit"]),
+                                                 shared_ff=int(sh.get("ff", 0)), shared_limit=float(sh.get("limit", 0.0))))
+            if not 1 <= kw["moe"].top <= kw["moe"].experts:
+                raise ValueError(f"Silatar: layer {i}: top {kw['moe'].top} of {kw['moe'].experts} experts")
+        else:
+            raise ValueError(f"Silatar: layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of the design")
+        layers.append(StackLayerSpec(**kw))
+    loop = doc.get("loop") or {}
+    spec = StackSpec(name=name, architecture="Silatar", width=int(doc["width"]), vocab=int(doc["vocab"]),
+                     layers=tuple(layers), loop_start=int(loop.get("start", 0)), loop_stop=int(loop.get("stop", 0)),
+                     loop_times=int(loop.get("times", 0)), norm_eps=float(doc["norm"]["eps"]), norm_offset=0.0,
+                     block="sandwich", norm_kind="layer", loop_mix=False,
+                     logit_softcap=float(doc.get("logit_softcap") or 0.0))
+    if spec.loop_times > 0 and not 0 <= spec.loop_start < spec.loop_stop <= len(layers):
+        raise ValueError(f"Silatar: loop {spec.loop_start}..{spec.loop_stop} does not fit {len(layers)} layers")
+    return spec
+
+
+def silatar_config(spec: StackSpec) -> dict:
+    """The config.json a Silatar StackSpec is read from (inverse of silatar_from_config)."""
+    doc = {"architecture": "Silatar", "layers": [], "logit_softcap": spec.logit_softcap, "norm": {"eps": spec.norm_eps},
+           "vocab": spec.vocab, "width": spec.width}
+    for L in spec.layers:
+        if L.mixer == "latent_attention":
+            a, r = L.latent, L.latent.rot
+            rot = {"base": r.base, "dims": r.dims}
+            if r.factor > 0:
+                rot["scaling"] = {"factor": r.factor, "fast": r.fast, "original": r.original, "slow": r.slow}
+            mixer = {"dim": a.dim, "heads": a.heads, "kv_rank": a.kv_rank, "rot": rot, "rot_dim": a.rot_dim,
+                     "scale": a.scale, "vdim": a.vdim}
+        else:
+            a = L.mlstm
+            mixer = {"dim": a.dim, "gate_cap": a.gate_cap, "heads": a.heads, "vdim": a.vdim}
+        if L.ff_kind == "moe":
+            mlp = {"expert": {"ff": L.moe.expert_ff, "limit": L.moe.limit}, "kind": "moe",
+                   "router": {"experts": L.moe.experts, "top": L.moe.top}}
+            if L.moe.shared_ff > 0:
+                mlp["shared"] = {"ff": L.moe.shared_ff, "limit": L.moe.shared_limit}
+        else:
+            mlp = {"ff": L.ff, "kind": "dense"} if L.ff > 0 else None
+        doc["layers"].append({"mixer": mixer, "mlp": mlp, "type": L.mixer})
+    if spec.loop_times > 0:
+        doc["loop"] = {"start": spec.loop_start, "stop": spec.loop_stop, "times": spec.loop_times}
+    return doc
+
+
+def silatar_tensor_shapes(spec: StackSpec) -> Dict[str, Tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a Silatar model (Linear weights are [out, in])."""
+    W, out = spec.width, {}
+    out["embed"] = (spec.vocab, W)
+    for i, L in enumerate(spec.layers):
+        p = f"l{i}."
+        out[p + "norm1"], out[p + "norm1b"] = (W,), (W,)
+        if L.mixer == "latent_attention":
+            a = L.latent
+            out[p + "mix.q"] = (a.heads * (a.dim + a.rot_dim), W)
+            out[p + "mix.dkv"] = (a.kv_rank + a.rot_dim, W)
+            out[p + "mix.dkv.norm"] = (a.kv_rank,)
+            out[p + "mix.uk"] = (a.heads * a.dim, a.kv_rank)
+            out[p + "mix.uv"] = (a.heads * a.vdim, a.kv_rank)
+            out[p + "mix.o"] = (W, a.heads * a.vdim)
+        else:
+            a = L.mlstm
+            out[p + "mix.q"], out[p + "mix.k"] = (a.heads * a.dim, W), (a.heads * a.dim, W)
+            out[p + "mix.v"], out[p + "mix.g"] = (a.heads * a.vdim, W), (a.heads * a.vdim, W)
+            out[p + "mix.o"] = (W, a.heads * a.vdim)
+            out[p + "mix.norm"] = (a.heads * a.vdim,)
+            for nm in ("i", "f"):
+                out[p + "mix." + nm], out[p + "mix." + nm + ".b"] = (a.heads, W), (a.heads,)
+        if L.ff_kind == "moe":
+            out[p + "norm2"], out[p + "norm2b"] = (W,), (W,)
+            for e in range(L.moe.experts):
+                q = f"{p}mlp.e{e}."
+                out[q + "gate"], out[q + "up"], out[q + "down"] = (L.moe.expert_ff, W), (L.moe.expert_ff, W), (W, L.moe.expert_ff)
+            out[p + "mlp.router"] = (L.moe.experts, W)
+            if L.moe.shared_ff > 0:
+                q = p + "mlp.shared."
+                out[q + "gate"], out[q + "up"], out[q + "down"] = (L.moe.shared_ff, W), (L.moe.shared_ff, W), (W, L.moe.shared_ff)
+                out[q + "sg"] = (1, W)
+        elif L.ff > 0:
+            out[p + "norm2"], out[p + "norm2b"] = (W,), (W,)
+            out[p + "mlp.up"], out[p + "mlp.down"] = (L.ff, W), (W, L.ff)
+    out["final.norm"] = (W,)
+    out["head"] = (spec.vocab, W)
+    return out
+
+
+def synth_silatar_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic Silatar checkpoint (bf16, checkpoint names): matrices N(0, std·√(64/in)), norm weights 1 + N(0, 0.1),
+    biases N(0, 1) (the forget gate's shifted up so that the memory keeps something)."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in silatar_tensor_shapes(spec).items():
+        if len(shape) == 1:
+            t = torch.randn(shape, generator=g)
+            t = t + 2.0 if name.endswith("f.b") else t if name.endswith(".b") else 1.0 + 0.1 * t
+        else:
+            t = torch.randn(shape, generator=g) * (std * (64.0 / shape[1]) ** 0.5)
+            if name.endswith("router"):
+                t = t * 4.0   # spread the scores so that the choice does not hang on the last bit
+        w[name] = t.to(torch.bfloat16)
+    return w
+
+
+def pack_silatar_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
+                         dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Checkpoint tensors (Silatar names) → the engine's layout on `device`.  Per layer: w_in = the mixer's in-projections
+    merged by rows (StackSpec.mix_layout), b_in fp32 (the mLSTM gates' biases), w_out = mix.o; latent attention: uk
+    transposed per head [heads, kv_rank, dim], uv as stored; dense feed-forward: up / down; experts: gate|up of all experts
+    as one [experts, 2·ff, width] block and down as [experts, width, ff]; shared expert: [gate | up | shared-gate row]
+    (padded to 8 rows) and down.  Vectors in fp32, matrices in `dtype`."""
+    W = spec.width
+    out: Dict[str, torch.Tensor] = {}
+
+    def mat(t):
+        return t.to(dtype).contiguous().to(device)
+
+    def vec(t):
+        return t.to(torch.float32).contiguous().to(device)
+
+    out["embed"], out["head"], out["final_norm"] = mat(named["embed"]), mat(named["head"]), vec(named["final.norm"])
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w_in = torch.zeros(lay.n_in, W, dtype=dtype)
+        b_in = torch.zeros(lay.n_in, dtype=torch.float32)
+
+        def put(off, name, bias=None):
+            t = named[p + name]
+            w_in[off:off + t.shape[0]] = t.to(dtype)
+            if bias is not None:
+                b_in[off:off + t.shape[0]] = named[p + bias].to(torch.float32)
+
+        if L.mixer == "latent_attention":
+            a = L.latent
+            put(lay.off_q, "mix.q")
+            put(lay.off_k, "mix.dkv")
+            out[p + "c_norm"] = vec(named[p + "mix.dkv.norm"])
+            out[p + "uk_t"] = mat(named[p + "mix.uk"].view(a.heads, a.dim, a.kv_rank).transpose(1, 2))
+            out[p + "uv"] = mat(named[p + "mix.uv"])
+        else:
+            a = L.mlstm
+            put(lay.off_q, "mix.q"), put(lay.off_k, "mix.k"), put(lay.off_v, "mix.v"), put(lay.off_g, "mix.g")
+            put(lay.off_gate, "mix.i", "mix.i.b")
+            put(lay.off_gate + a.heads, "mix.f", "mix.f.b")
+            out[p + "head_norm"] = vec(named[p + "mix.norm"])
+        out[p + "w_in"], out[p + "b_in"], out[p + "w_out"] = w_in.to(device), b_in.to(device), mat(named[p + "mix.o"])
+        out[p + "norm"], out[p + "post_norm"] = vec(named[p + "norm1"]), vec(named[p + "norm1b"])
+        if L.ff_kind == "moe" or L.ff > 0:
+            out[p + "ff_norm"], out[p + "ff_post_norm"] = vec(named[p + "norm2"]), vec(named[p + "norm2b"])
+        if L.ff_kind == "moe":
+            m, q = L.moe, p + "mlp."
+            out[p + "router"] = mat(named[q + "router"])
+            out[p + "w_exp_in"] = mat(torch.stack([torch.cat([named[f"{q}e{e}.gate"], named[f"{q}e{e}.up"]], 0)
+                                                   for e in range(m.experts)]))
+            out[p + "w_exp_out"] = mat(torch.stack([named[f"{q}e{e}.down"] for e in range(m.experts)]))
+            if m.shared_ff > 0:
+                sh = torch.zeros(_up8(2 * m.shared_ff + 1), W, dtype=dtype)
+                sh[:m.shared_ff] = named[q + "shared.gate"].to(dtype)
+                sh[m.shared_ff:2 * m.shared_ff] = named[q + "shared.up"].to(dtype)
+                sh[2 * m.shared_ff] = named[q + "shared.sg"].to(dtype)[0]
+                out[p + "w_ff_in"], out[p + "w_ff_out"] = sh.to(device), mat(named[q + "shared.down"])
+        elif L.ff > 0:
+            out[p + "w_ff_in"], out[p + "w_ff_out"] = mat(named[p + "mlp.up"]), mat(named[p + "mlp.down"])
+    return out
+
+
+@dataclass(frozen=True)
+class Architecture:
+    """One design of the layer-stack registry: its config reader and writer, checkpoint tensor list, synthetic checkpoint
+    and the packer into the engine's layout."""
+    from_config: Callable[[dict], StackSpec]
+    to_config: Callable[[StackSpec], dict]
+    tensor_shapes: Callable[[StackSpec], Dict[str, Tuple[int, ...]]]
+    synth_weights: Callable[..., Dict[str, torch.Tensor]]
+    pack: Callable[..., Dict[str, torch.Tensor]]
+
+    def __call__(self, doc: dict) -> StackSpec:
+        return self.from_config(doc)
+
+
+# config.json "architecture" → design.  (The Llama-family checkpoints are told apart by "model_type": loader.py.)
+ARCHITECTURES: Dict[str, Architecture] = {}
 
 
 def kozusun_config(spec: StackSpec) -> dict:
@@ -416,6 +753,38 @@ def pack_stack_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="
             out[p + "side_proj"] = mat(named[p + "side.proj"])
             out[p + "side_norm"] = vec(named[p + "side.norm"])
     return out
+
+
+def pack_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
+                 dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Checkpoint tensors of any registered design → the engine's layout."""
+    return ARCHITECTURES[spec.architecture].pack(spec, named, device=device, dtype=dtype)
+
+
+def save_stack_checkpoint(spec: StackSpec, named: Dict[str, torch.Tensor], out_dir: str) -> None:
+    """config.json + model.safetensors (bf16) of a layer-stack model, as loader.load_model reads them."""
+    d = Path(out_dir)
+    d.mkdir(parents=True, exist_ok=True)
+    (d / "config.json").write_text(json.dumps(ARCHITECTURES[spec.architecture].to_config(spec), indent=1))
+    header, off, blobs = {}, 0, []
+    for name in sorted(named):
+        raw = named[name].detach().to("cpu").to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = {"dtype": "BF16", "shape": list(named[name].shape), "data_offsets": [off, off + len(raw)]}
+        off += len(raw)
+        blobs.append(raw)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(d / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+ARCHITECTURES["Kozusun"] = Architecture(kozusun_from_config, kozusun_config, kozusun_tensor_shapes, synth_kozusun_weights,
+                                        pack_stack_weights)
+ARCHITECTURES["Silatar"] = Architecture(silatar_from_config, silatar_config, silatar_tensor_shapes, synth_silatar_weights,
+                                        pack_silatar_weights)
 
 
 # ------------------------------------------------------------------------------------------- checkpoint writer
