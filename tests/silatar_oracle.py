@@ -85,20 +85,16 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mixer:
 
 
 # --------------------------------------------------------------------------------------------------------------- mLSTM
-def mlstm(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mixer: dict, eps: float) -> torch.Tensor:
-    """Matrix memory per head, token by token: S [dim, vdim], n [dim], running maximum m (starting at 0)."""
-    T = h.shape[0]
-    H, dk, dv, cap = mixer["heads"], mixer["dim"], mixer["vdim"], float(mixer["gate_cap"])
-    q = (h @ w[p + "q"].T).view(T, H, dk) * dk ** -0.5
-    k = (h @ w[p + "k"].T).view(T, H, dk)
-    v = (h @ w[p + "v"].T).view(T, H, dv)
-    gi = cap * torch.tanh((h @ w[p + "i"].T + w[p + "i.b"]) / cap)                            # log input gate [T, H]
-    gf = F.logsigmoid(cap * torch.tanh((h @ w[p + "f"].T + w[p + "f.b"]) / cap))              # log forget gate
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
+def mlstm_cell(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gi: torch.Tensor, gf: torch.Tensor) -> torch.Tensor:
+    """The recurrence alone.  q (already scaled), k [T, H, dk]; v [T, H, dv]; log gates gi, gf [T, H] → [T, H, dv].
+    Per head: S [dk, dv], n [dk] and the running maximum m all start at 0."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    out = torch.zeros(T, H, dv, dtype=q.dtype)
     for hd in range(H):
-        S = torch.zeros(dk, dv, dtype=h.dtype)
-        n = torch.zeros(dk, dtype=h.dtype)
-        m = torch.zeros((), dtype=h.dtype)
+        S = torch.zeros(dk, dv, dtype=q.dtype)
+        n = torch.zeros(dk, dtype=q.dtype)
+        m = torch.zeros((), dtype=q.dtype)
         for t in range(T):
             m_new = torch.maximum(gf[t, hd] + m, gi[t, hd])
             a, b = torch.exp(gf[t, hd] + m - m_new), torch.exp(gi[t, hd] - m_new)
@@ -107,6 +103,23 @@ def mlstm(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mixer: dict, eps:
             m = m_new
             den = torch.maximum((n * q[t, hd]).sum().abs(), torch.exp(-m)) + 1e-6
             out[t, hd] = (S.T @ q[t, hd]) / den
+    return out
+
+
+def capped(z: torch.Tensor, cap: float) -> torch.Tensor:
+    return cap * torch.tanh(z / cap)
+
+
+def mlstm(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mixer: dict, eps: float) -> torch.Tensor:
+    """Matrix memory per head, token by token, then a unit-rms norm per head, a weight, an output gate and a projection."""
+    T = h.shape[0]
+    H, dk, dv, cap = mixer["heads"], mixer["dim"], mixer["vdim"], float(mixer["gate_cap"])
+    q = (h @ w[p + "q"].T).view(T, H, dk) * dk ** -0.5
+    k = (h @ w[p + "k"].T).view(T, H, dk)
+    v = (h @ w[p + "v"].T).view(T, H, dv)
+    gi = capped(h @ w[p + "i"].T + w[p + "i.b"], cap)                                         # log input gate [T, H]
+    gf = F.logsigmoid(capped(h @ w[p + "f"].T + w[p + "f.b"], cap))                           # log forget gate
+    out = mlstm_cell(q, k, v, gi, gf)
     o = unit_rms(out, eps).reshape(T, H * dv) * w[p + "norm"]
     return (o * torch.sigmoid(h @ w[p + "g"].T)) @ w[p + "o"].T
 

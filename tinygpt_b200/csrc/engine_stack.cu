@@ -1089,6 +1089,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     B200_CUDA(cudaDeviceGetAttribute(&s->num_sms, cudaDevAttrMultiProcessorCount, dev));
   }
   s->plans.resize(d.n_layers);
+  s->splans.resize(d.n_layers);
   s->fast = d.dtype == B200_BF16 && !env_flag("B200_STACK_PLAIN", false);
   if (s->fast) {
     if ((rc = gemv_setup_attributes()) != B200_OK || (rc = gemv_batch_setup_attributes()) != B200_OK) return rc;
@@ -1105,7 +1106,6 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
                             plan(&s->plans[l].side_gate, L.side_gate, d.side_dim, d.width, EPI_ACT_TABLE, PRO_F32) &&
                             plan(&s->plans[l].side_proj, L.side_proj, d.width, d.side_dim, EPI_BIAS_F32);
     }
-    s->splans.resize(d.n_layers);
     for (int l = 0; sandwich && l < d.n_layers; ++l) {
       const b200_stack_layer& L = s->layers[l];
       StackEngine::SPlans& sp = s->splans[l];

@@ -274,7 +274,15 @@ def stack_act_mul(g: torch.Tensor, u: torch.Tensor, act: str = "gelu_tanh") -> t
         raise B200Error("stack_act_mul: g and u must be equally shaped column slices of one row-major matrix")
     y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
     check(lib().b200_stack_act_mul(y.data_ptr(), y.stride(0), g.data_ptr(), u.data_ptr(), g.stride(0), g.shape[0],
-                                   g.shape[1], {"gelu_tanh": 0, "silu": 1}[act], _sdt(g), _stream()), "b200_stack_act_mul")
+                                   g.shape[1], {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}[act], _sdt(g), _stream()), "b200_stack_act_mul")
+    return y
+
+
+def stack_act(g: torch.Tensor, act: str = "gelu_erf") -> torch.Tensor:
+    """T( act(g) ) elementwise over a row-major [rows, n]."""
+    y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
+    check(lib().b200_stack_act_mul(y.data_ptr(), y.stride(0), g.data_ptr(), None, g.stride(0), g.shape[0], g.shape[1],
+                                   {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}[act], _sdt(g), _stream()), "b200_stack_act_mul")
     return y
 
 
@@ -284,3 +292,89 @@ def stack_rms_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float,
     check(lib().b200_stack_rms_add(x.data_ptr(), y.data_ptr(), w.data_ptr(), x.numel() // x.shape[-1], x.shape[-1],
                                    float(eps), float(mult), _stream()), "b200_stack_rms_add")
     return x
+
+
+# ---- mechanisms of sandwich blocks (csrc/stack_mix.cu)
+_NORM_KINDS = {"rms": 0, "layer": 1}
+
+
+def stack_norm(x: torch.Tensor, w: torch.Tensor, eps: float, kind: str = "layer",
+               out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """out_dtype( norm(x)·w ) for fp32 x [rows, dim]: kind "layer" = (x − mean)·rsqrt(var + eps), "rms" = x·rsqrt(mean(x²) + eps)."""
+    x, w = _chk(x, "stack_norm x", torch.float32), _chk(w, "stack_norm w", torch.float32)
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    check(lib().b200_stack_norm(y.data_ptr(), None, x.data_ptr(), w.data_ptr(), x.numel() // x.shape[-1], x.shape[-1],
+                                float(eps), _NORM_KINDS[kind], 0, _sdt(y), _stream()), "b200_stack_norm")
+    return y
+
+
+def stack_norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, kind: str = "layer") -> torch.Tensor:
+    """x += norm(y)·w in place on fp32 x [rows, dim]; returns x."""
+    x, y, w = (_chk(t, "stack_norm_add", torch.float32) for t in (x, y, w))
+    check(lib().b200_stack_norm(None, x.data_ptr(), y.data_ptr(), w.data_ptr(), x.numel() // x.shape[-1], x.shape[-1],
+                                float(eps), _NORM_KINDS[kind], 1, 1, _stream()), "b200_stack_norm")
+    return x
+
+
+def stack_glu_clamp(gu: torch.Tensor, limit: float) -> torch.Tensor:
+    """gu [rows, 2n] = [g | u] → T( min(g, limit)·sigmoid(1.702·min(g, limit))·(clamp(u, ±limit) + 1) ) [rows, n]."""
+    gu = _chk(gu, "stack_glu_clamp", gu.dtype)
+    n = gu.shape[1] // 2
+    y = torch.empty(gu.shape[0], n, dtype=gu.dtype, device=gu.device)
+    check(lib().b200_stack_glu_clamp(y.data_ptr(), gu.data_ptr(), gu.shape[0], n, float(limit), _sdt(gu), _stream()),
+          "b200_stack_glu_clamp")
+    return y
+
+
+def stack_latent_attention(proj: torch.Tensor, off_down: int, cache: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor, *,
+                           heads, dim, rot_dim, vdim, kv_rank, scale, rot_dims, c_norm: torch.Tensor, uk_t: torch.Tensor,
+                           uv: torch.Tensor, rot_table: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """Latent attention of n_tok rows of proj = [q | down] over the slots' caches [slots, ctx, kv_rank + rot_dim] (the new
+    rows are written first) → [n_tok, heads·vdim].  uk_t [heads, kv_rank, dim], uv [heads·vdim, kv_rank] of proj's dtype."""
+    import ctypes as C
+    from ._lib import LatentDesc
+    a = _attn_desc(heads, 1, dim, vdim, scale, 0, 0, 0)
+    l = LatentDesc(int(kv_rank), int(rot_dim), int(rot_dims), c_norm.data_ptr(), uk_t.data_ptr(), uv.data_ptr(), _ptr(rot_table))
+    out = torch.empty(proj.shape[0], heads * vdim, dtype=proj.dtype, device=proj.device)
+    check(lib().b200_stack_latent_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), int(off_down),
+                                            cache.data_ptr(), cache.stride(0), slot.data_ptr(), pos.data_ptr(), proj.shape[0],
+                                            C.byref(a), C.byref(l), float(eps), _sdt(proj), _stream()),
+          "b200_stack_latent_attention")
+    return out
+
+
+def stack_mlstm_state(slots: int, heads: int, dim: int, vdim: int, device) -> torch.Tensor:
+    """Zeroed fp32 state [slots, floats per slot] of one mLSTM run."""
+    return torch.zeros(slots, int(lib().b200_stack_mlstm_state_floats(heads, dim, vdim)), dtype=torch.float32, device=device)
+
+
+def stack_mlstm(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, gates: torch.Tensor, state: torch.Tensor,
+                row0: torch.Tensor, count: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor, *, heads, dim, vdim,
+                gate_cap) -> torch.Tensor:
+    """mLSTM recurrence over the sequences {row0, count} of proj's rows (slot / pos per row), continuing `state` →
+    fp32 [rows, heads, vdim + 2]: numerators, n·q, m."""
+    import ctypes as C
+    a = _attn_desc(heads, heads, dim, vdim, 1.0, 0, 0, 0)
+    gates = _chk(gates, "stack_mlstm gates", torch.float32)
+    out = torch.zeros(proj.shape[0], heads, vdim + 2, dtype=torch.float32, device=proj.device)
+    check(lib().b200_stack_mlstm(out.data_ptr(), proj.data_ptr(), proj.stride(0), off_q, off_k, off_v, gates.data_ptr(),
+                                 state.data_ptr(), state.stride(0), row0.data_ptr(), count.data_ptr(), slot.data_ptr(),
+                                 pos.data_ptr(), row0.shape[0], proj.shape[0], C.byref(a), float(gate_cap), _sdt(proj),
+                                 _stream()), "b200_stack_mlstm")
+    return out
+
+
+def stack_moe(h: torch.Tensor, router: torch.Tensor, w_exp_in: torch.Tensor, w_exp_out: torch.Tensor, top: int, limit: float):
+    """Routed experts on h [rows, width]: router [E, width], w_exp_in [E, 2·ff, width] (gate | up), w_exp_out [E, width, ff]
+    → (y fp32 [rows, width], chosen int32 [rows, top], scores fp32 [rows, top])."""
+    import ctypes as C
+    from ._lib import MoeDesc
+    h = _chk(h, "stack_moe h", h.dtype)
+    E, ff2, W = w_exp_in.shape
+    m = MoeDesc(E, int(top), ff2 // 2, 0, float(limit), 0.0, router.data_ptr(), w_exp_in.data_ptr(), w_exp_out.data_ptr())
+    y = torch.empty(h.shape[0], W, dtype=torch.float32, device=h.device)
+    chosen = torch.empty(h.shape[0], top, dtype=torch.int32, device=h.device)
+    scores = torch.empty(h.shape[0], top, dtype=torch.float32, device=h.device)
+    check(lib().b200_stack_moe(y.data_ptr(), h.data_ptr(), h.shape[0], W, C.byref(m), chosen.data_ptr(), scores.data_ptr(),
+                               _sdt(h), _stream()), "b200_stack_moe")
+    return y, chosen, scores
