@@ -677,7 +677,16 @@ def main():
     ap.add_argument("--stack-compare", nargs="?", const="all", default=None, metavar="SIZES",
                     help="instead of the headline run: prefill / decode throughput of the Kozusun layer-stack design beside "
                          "the Llama-family model of equal size (comma-separated sizes of tinygpt_b200/stack_bench.py, or all)")
+    ap.add_argument("--silatar-compare", nargs="?", const="all", default=None, metavar="SIZES",
+                    help="instead of the headline run: prefill / decode throughput of the Silatar layer-stack design (latent "
+                         "attention, mLSTM, routed experts) beside the Kozusun design of equal width, vocabulary, layer runs "
+                         "and matrix parameters per token (sizes of tinygpt_b200/stack_bench.py, or all)")
     args = ap.parse_args()
+    if args.silatar_compare is not None:
+        from tinygpt_b200 import build, stack_bench
+        build.build()
+        stack_bench.main_silatar(args.silatar_compare, steps=max(1, min(args.steps, 10)), warmup=max(3, args.warmup))
+        return
     if args.stack_compare is not None:
         from tinygpt_b200 import build, stack_bench
         build.build()

@@ -111,6 +111,9 @@ struct StackEngine {
   float *projf = nullptr, *rec_o = nullptr, *y2 = nullptr;
   int32_t *m_seg_row0 = nullptr, *m_seg_count = nullptr;
   MoeRun moe_ws{};                 // the routing workspace's pointers
+  float* lat_ws = nullptr;         // split-key partials of decode-shaped latent attention
+  unsigned int* lat_tickets = nullptr;
+  int lat_heads_max = 0, lat_rank_max = 0;
   int qa_max = 0, ol_max = 0, rec_o_max = 0, moe_e_max = 0, moe_top_max = 0, moe_ff_max = 0, lin_max = 0;
   bool any_rec = false, any_moe = false;
   struct SPlans {
@@ -205,6 +208,8 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_ms = take(s->any_moe ? P * 4 : 0), o_ma = take(s->any_moe ? P * W * s->esz : 0);
   const size_t o_mg = take(s->any_moe ? P * 2 * s->moe_ff_max * s->esz : 0), o_mc = take(s->any_moe ? P * s->moe_ff_max * s->esz : 0);
   const size_t o_mo = take(s->any_moe ? P * W * 4 : 0);
+  const size_t o_lw = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * s->lat_heads_max * kLatentMaxSplits * (2 + s->lat_rank_max) * 4 : 0);
+  const size_t o_lt2 = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * 4 : 0);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->ws_tok = tok;
@@ -242,6 +247,8 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->moe_ws.gu = s->ws + o_mg;
   s->moe_ws.act = s->ws + o_mc;
   s->moe_ws.outp = (float*)(s->ws + o_mo);
+  s->lat_ws = s->lat_rank_max > 0 ? (float*)(s->ws + o_lw) : nullptr;
+  s->lat_tickets = (unsigned int*)(s->ws + o_lt2);
   s->cat = (__nv_bfloat16*)(s->ws + o_cat);
   s->attn_ws = (float*)(s->ws + o_aws);
   s->attn_tickets = (unsigned int*)(s->ws + o_tick);
@@ -538,6 +545,12 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     a.cache = s->kbase + s->run_k_off[r] * esz; a.slot_stride = (int64_t)s->k_slot;
     a.slot = s->m_slot; a.pos = s->m_pos; a.n_tok = n_tok;
     a.qa = s->qa; a.ol = s->ol; a.out = s->mid; a.ld_out = L.k_out;
+    if (n_tok <= kSmallRows && s->lat_ws != nullptr) {   // splits follow the context the engine was built for, not the
+      a.split_ws = s->lat_ws;                             // positions of the moment: a captured step stays valid
+      a.split_tickets = s->lat_tickets;
+      a.nsplit = std::min(kLatentMaxSplits, (d.max_ctx + kLatentSplitKeys - 1) / kLatentSplitKeys);
+      a.keys_per_split = ((d.max_ctx + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
+    }
     if ((rc = run_latent_attention(a, dt, st)) != B200_OK) return rc;
   } else {
     const int H = L.attn.heads;
@@ -548,11 +561,19 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
       m.gates = s->projf + L.off_gate; m.ld_gates = L.n_in;
     } else {
       float* gates = s->projf + (size_t)kMaxBatch * s->n_in_max;
+      if (n_tok <= kSmallRows) {
+        SmallGemv g;
+        g.a = s->h; g.lda = W; g.w = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz;
+        g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
+        g.c = gates; g.ldc = 2 * H; g.c_f32 = true; g.M = n_tok; g.N = 2 * H; g.K = W; g.items = 1;
+        if ((rc = launch_small_gemv(g, dt, st)) != B200_OK) return rc;
+      } else {
       StackGemm g;
       g.a = s->h; g.lda = W; g.k1 = W;
       g.w = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz; g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
       g.M = n_tok; g.N = 2 * H; g.K = W; g.epi = SEPI_STORE_F32; g.c = gates; g.ldc = 2 * H;
       if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      }
       m.gates = gates; m.ld_gates = 2 * H;
     }
     m.state = s->rstate + s->run_s_off[r]; m.slot_stride = (int64_t)s->s_slot;
@@ -579,6 +600,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   }
   MoeRun m = s->moe_ws;
   m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
+  m.small = n_tok <= kSmallRows;
   if (L.moe.shared_ff > 0) {
     const int fs = L.moe.shared_ff, n_sh = up8i(2 * fs + 1);
     if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, n_sh, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
@@ -1004,6 +1026,8 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
                      "engine_create_stack: layer %d: segment offsets do not fit", l);
       s->qa_max = std::max(s->qa_max, a.heads * (q.kv_rank + q.rot_dim));
       s->ol_max = std::max(s->ol_max, a.heads * q.kv_rank);
+      s->lat_heads_max = std::max(s->lat_heads_max, a.heads);
+      s->lat_rank_max = std::max(s->lat_rank_max, q.kv_rank);
     } else {
       B200_CHECK_ARG(a.dim <= kMlstmMaxDim && L.rec.gate_cap > 0.f && L.rec.head_norm, "engine_create_stack: layer %d: mLSTM description", l);
       B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.heads * a.dim <= L.n_in &&

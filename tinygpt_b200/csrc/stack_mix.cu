@@ -201,19 +201,190 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------- small products
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  unpack8(*reinterpret_cast<const uint4*>(p), v);
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// One warp per output row n of item blockIdx.y.  VEC: 16-byte (bf16) / 32-byte (fp32) pieces of the matrix row and of
+// the M activation rows, lane l takes pieces l, l + 32, …; otherwise element by element.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31, z = blockIdx.y;
+  if (n >= g.N) return;
+  const int64_t mat = g.item_mat != nullptr ? g.item_mat[z] : z;
+  const T* wr = static_cast<const T*>(g.w) + mat * g.sw + (int64_t)n * g.K;
+  const T* a = static_cast<const T*>(g.a) + (int64_t)z * g.sa;
+  float acc[kSmallRows];
+#pragma unroll
+  for (int m = 0; m < kSmallRows; ++m) acc[m] = 0.f;
+  if constexpr (VEC) {
+    for (int k = lane * 8; k < g.K; k += 256) {
+      float wv[8];
+      load8<T>(wr + k, wv);
+#pragma unroll
+      for (int m = 0; m < kSmallRows; ++m) {
+        if (m < g.M) {
+          float av[8];
+          load8<T>(a + (int64_t)m * g.lda + k, av);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[m] = fmaf(wv[i], av[i], acc[m]);
+        }
+      }
+    }
+  } else {
+    for (int k = lane; k < g.K; k += 32) {
+      const float wv = ldf<T>(wr + k);
+#pragma unroll
+      for (int m = 0; m < kSmallRows; ++m)
+        if (m < g.M) acc[m] = fmaf(wv, ldf<T>(a + (int64_t)m * g.lda + k), acc[m]);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < kSmallRows; ++m) {
+    if (m >= g.M) break;
+    float v = warp_sum(acc[m]);
+    if (lane == 0) {
+      if (g.bias != nullptr) v += g.bias[n];
+      const int64_t o = (int64_t)m * g.ldc + (int64_t)z * g.sc + n;
+      if (g.c_f32) static_cast<float*>(g.c)[o] = v;
+      else static_cast<T*>(g.c)[o] = cvt<T>(v);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------- latent attention, decode-shaped
+// One CTA of eight warps per (row, split of the key list).  The split's key rows [c | rotated key part] are staged in
+// shared memory 32 at a time and serve ALL heads (warp w takes heads w, w + 8, …): the rows are read from memory once per
+// row of the step instead of once per head.  Per head and chunk: 32 scores (every key's dot product by the whole warp),
+// the online softmax, the weighted latents.  Partials go to split_ws; the CTA that takes a row's last ticket merges
+// the splits of every head (non-blocking: nobody waits for anybody).
+constexpr int kLatHeadsPerWarp = 4;   // heads <= 32
+template <typename T>
+__global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun p) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float sm[];
+  __shared__ unsigned int s_ticket;
+  const int t = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = p.l.kv_rank, kd = r + p.l.rot_dim, H = p.a.heads;
+  float* q = sm;                          // [H][kd], scaled
+  float* kc = sm + (size_t)H * kd;        // [32][kd] staged key rows
+  const T* qrow = static_cast<const T*>(p.qa) + (int64_t)t * H * kd;
+  for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
+  const int n_keys = p.pos[t] + 1;
+  const int k_lo = split * p.keys_per_split, k_hi = min(n_keys, k_lo + p.keys_per_split);
+  const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
+  float m[kLatHeadsPerWarp], sum[kLatHeadsPerWarp], acc[kLatHeadsPerWarp][kLatVR];
+#pragma unroll
+  for (int u = 0; u < kLatHeadsPerWarp; ++u) {
+    m[u] = -INFINITY;
+    sum[u] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kLatVR; ++i) acc[u][i] = 0.f;
+  }
+  for (int j0 = k_lo; j0 < k_hi; j0 += 32) {
+    const int cnt = min(32, k_hi - j0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < cnt * kd; i += blockDim.x) kc[i] = ldf<T>(K + (int64_t)j0 * kd + i);
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < kLatHeadsPerWarp; ++u) {
+      const int hd = warp + 8 * u;
+      if (hd >= H) break;
+      const float* qh = q + (size_t)hd * kd;
+      float s_mine = -INFINITY;
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float* kr = kc + (size_t)jj * kd;
+        float d = 0.f;
+        for (int i = lane; i < kd; i += 32) d = fmaf(qh[i], kr[i], d);
+        d = warp_sum(d);
+        if (lane == jj) s_mine = d;
+      }
+      const float m_new = fmaxf(m[u], warp_max(s_mine));
+      const float pr = lane < cnt ? expf(s_mine - m_new) : 0.f;
+      const float corr = expf(m[u] - m_new);
+      sum[u] = sum[u] * corr + warp_sum(pr);
+#pragma unroll
+      for (int i = 0; i < kLatVR; ++i) acc[u][i] *= corr;
+      for (int jj = 0; jj < cnt; ++jj) {
+        const float pj = __shfl_sync(0xffffffffu, pr, jj);
+        const float* kr = kc + (size_t)jj * kd;
+#pragma unroll
+        for (int i = 0; i < kLatVR; ++i)
+          if (lane + 32 * i < r) acc[u][i] = fmaf(pj, kr[lane + 32 * i], acc[u][i]);
+      }
+      m[u] = m_new;
+    }
+  }
+  // partials of this split
+#pragma unroll
+  for (int u = 0; u < kLatHeadsPerWarp; ++u) {
+    const int hd = warp + 8 * u;
+    if (hd >= H) break;
+    float* dst = p.split_ws + (((int64_t)t * H + hd) * p.nsplit + split) * (2 + r);
+    if (lane == 0) {
+      dst[0] = m[u];
+      dst[1] = sum[u];
+    }
+#pragma unroll
+    for (int i = 0; i < kLatVR; ++i)
+      if (lane + 32 * i < r) dst[2 + lane + 32 * i] = acc[u][i];
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_ticket = atomicAdd(p.split_tickets + t, 1u);
+  __syncthreads();
+  if (s_ticket != (unsigned)p.nsplit - 1) return;
+  __threadfence();
+  if (threadIdx.x == 0) p.split_tickets[t] = 0;   // ready for the next launch
+  for (int hd = warp; hd < H; hd += 8) {
+    const float* src = p.split_ws + ((int64_t)t * H + hd) * p.nsplit * (2 + r);
+    float M = -INFINITY;
+    for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, __ldcg(src + (int64_t)sp * (2 + r)));
+    float tot = 0.f, out[kLatVR];
+#pragma unroll
+    for (int i = 0; i < kLatVR; ++i) out[i] = 0.f;
+    for (int sp = 0; sp < p.nsplit; ++sp) {
+      const float* ps = src + (int64_t)sp * (2 + r);
+      const float ms = __ldcg(ps);
+      if (ms == -INFINITY) continue;
+      const float f = expf(ms - M);
+      tot += f * __ldcg(ps + 1);
+#pragma unroll
+      for (int i = 0; i < kLatVR; ++i)
+        if (lane + 32 * i < r) out[i] = fmaf(f, __ldcg(ps + 2 + lane + 32 * i), out[i]);
+    }
+    T* orow = static_cast<T*>(p.ol) + ((int64_t)t * H + hd) * r;
+#pragma unroll
+    for (int i = 0; i < kLatVR; ++i)
+      if (lane + 32 * i < r) orow[lane + 32 * i] = cvt<T>(out[i] / tot);
+  }
+}
+
 // --------------------------------------------------------------------------------------------------------------- mLSTM
 // One warp per (sequence, head, state column): lane l holds rows l, l + 32, … of its column of S; column vdim is the
 // normaliser n (the column whose "value" is 1).  Every warp carries its own copy of the running maximum m, so columns
 // never read what another column's warp wrote.  Per token: the capped gates, m_t = max(f + m, i), the column's decay and
 // update, then the column's dot with q (a numerator of the output, or n·q).  The next token's operands are requested
 // while the current one is summed.  Eight columns per CTA.
-constexpr int kRecDR = kMlstmMaxDim / 32;
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T>
+// DR = rows of S per lane (key size <= 32·DR).  Tokens are taken four at a time: while one group is summed, the next
+// group's q, k, v and gate logits are already on their way into registers, so the walk along the sequence waits for
+// memory once per sequence, not once per token.
+template <typename T, int DR>
 __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
   pdl_trigger();
   pdl_wait();
+  constexpr int PF = DR >= 16 ? 2 : 4;
   const int seg = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int dk = p.a.dim, dv = p.a.vdim, H = p.a.heads;
   const int j = blockIdx.z * 8 + warp;
@@ -223,56 +394,70 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
   const int pos0 = p.pos[r0];
   float* st = p.state + (int64_t)p.slot[r0] * p.slot_stride + (int64_t)hd * ((int64_t)dk * (dv + 1) + dv + 1);
   float* st_m = st + (int64_t)dk * (dv + 1);
-  float S[kRecDR], m = 0.f;
+  float S[DR], m = 0.f;
 #pragma unroll
-  for (int i = 0; i < kRecDR; ++i) {
+  for (int i = 0; i < DR; ++i) {
     const int d = lane + 32 * i;
     S[i] = (pos0 > 0 && d < dk) ? st[(int64_t)d * (dv + 1) + j] : 0.f;
   }
   if (pos0 > 0) m = st_m[j];
   const float qs = rsqrtf((float)dk), cap = p.gate_cap;
   const T* P = static_cast<const T*>(p.proj);
-  float qn[kRecDR], kn[kRecDR], vn = 1.f, zi = 0.f, zf = 0.f;
-  auto fetch = [&](int row) {
+  struct Tok {
+    float q[DR], k[DR], v, zi, zf;
+  };
+  Tok cur[PF], nxt[PF];
+  auto fetch = [&](Tok& o, int t) {
+    const bool ok = t < cnt;
+    const int row = r0 + (ok ? t : 0);
     const T* pr = P + (int64_t)row * p.ld_proj;
 #pragma unroll
-    for (int i = 0; i < kRecDR; ++i) {
+    for (int i = 0; i < DR; ++i) {
       const int d = lane + 32 * i;
-      qn[i] = d < dk ? ldf<T>(pr + p.off_q + hd * dk + d) : 0.f;
-      kn[i] = d < dk ? ldf<T>(pr + p.off_k + hd * dk + d) : 0.f;
+      o.q[i] = (ok && d < dk) ? ldf<T>(pr + p.off_q + hd * dk + d) : 0.f;
+      o.k[i] = (ok && d < dk) ? ldf<T>(pr + p.off_k + hd * dk + d) : 0.f;
     }
-    vn = j < dv ? ldf<T>(pr + p.off_v + hd * dv + j) : 1.f;
-    zi = p.gates[(int64_t)row * p.ld_gates + hd];
-    zf = p.gates[(int64_t)row * p.ld_gates + H + hd];
+    o.v = (ok && j < dv) ? ldf<T>(pr + p.off_v + hd * dv + j) : 1.f;
+    o.zi = ok ? p.gates[(int64_t)row * p.ld_gates + hd] : 0.f;
+    o.zf = ok ? p.gates[(int64_t)row * p.ld_gates + H + hd] : 0.f;
   };
-  fetch(r0);
-  for (int t = 0; t < cnt; ++t) {
-    float qc[kRecDR], kc[kRecDR];
 #pragma unroll
-    for (int i = 0; i < kRecDR; ++i) {
-      qc[i] = qn[i] * qs;
-      kc[i] = kn[i];
-    }
-    const float v = vn, gi = cap * tanhf(zi / cap), gf = log_sigmoid(cap * tanhf(zf / cap));
-    if (t + 1 < cnt) fetch(r0 + t + 1);
-    const float m_new = fmaxf(gf + m, gi);
-    const float a = expf(gf + m - m_new), b = expf(gi - m_new) * v;
-    float dot = 0.f;
+  for (int u = 0; u < PF; ++u) fetch(nxt[u], u);
+  for (int g0 = 0; g0 < cnt; g0 += PF) {
 #pragma unroll
-    for (int i = 0; i < kRecDR; ++i) {
-      S[i] = fmaf(a, S[i], b * kc[i]);
-      dot = fmaf(S[i], qc[i], dot);
+    for (int u = 0; u < PF; ++u) cur[u] = nxt[u];
+    if (g0 + PF < cnt) {
+#pragma unroll
+      for (int u = 0; u < PF; ++u) fetch(nxt[u], g0 + PF + u);
     }
-    dot = warp_sum(dot);
-    m = m_new;
-    if (lane == 0) {
-      float* orow = p.o + ((int64_t)(r0 + t) * H + hd) * (dv + 2);
-      orow[j] = dot;
-      if (j == dv) orow[dv + 1] = m;
+    float gi[PF], gf[PF];
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+      gi[u] = cap * tanhf(cur[u].zi / cap);
+      gf[u] = log_sigmoid(cap * tanhf(cur[u].zf / cap));
+    }
+#pragma unroll
+    for (int u = 0; u < PF; ++u) {
+      if (g0 + u >= cnt) break;
+      const float m_new = fmaxf(gf[u] + m, gi[u]);
+      const float a = expf(gf[u] + m - m_new), b = expf(gi[u] - m_new) * cur[u].v;
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < DR; ++i) {
+        S[i] = fmaf(a, S[i], b * cur[u].k[i]);
+        dot = fmaf(S[i], cur[u].q[i] * qs, dot);
+      }
+      dot = warp_sum(dot);
+      m = m_new;
+      if (lane == 0) {
+        float* orow = p.o + ((int64_t)(r0 + g0 + u) * H + hd) * (dv + 2);
+        orow[j] = dot;
+        if (j == dv) orow[dv + 1] = m;
+      }
     }
   }
 #pragma unroll
-  for (int i = 0; i < kRecDR; ++i) {
+  for (int i = 0; i < DR; ++i) {
     const int d = lane + 32 * i;
     if (d < dk) st[(int64_t)d * (dv + 1) + j] = S[i];
   }
@@ -340,7 +525,8 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const MoeRun p) {
     if (lane == 0) {
       p.sel_e[(int64_t)t * top + k] = bi;
       p.sel_w[(int64_t)t * top + k] = 1.f / (1.f + expf(-bv));
-      atomicAdd(p.plan + bi, 1);
+      if (p.small) p.pair_slot[(int64_t)t * top + k] = t * top + k;   // no sorting: a pair stays where it is
+      else atomicAdd(p.plan + bi, 1);
     }
     last_v = bv;
     last_i = bi;
@@ -467,6 +653,25 @@ int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total,
   return B200_OK;
 }
 
+int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(g.a && g.w && g.c && g.M >= 1 && g.M <= kSmallRows && g.N > 0 && g.K > 0 && g.items > 0 && g.items <= 65535,
+                 "small gemv: bad arguments M=%d N=%d K=%d items=%d", g.M, g.N, g.K, g.items);
+  const size_t esz = dtype == B200_F32 ? 4 : 2;
+  const size_t al = dtype == B200_F32 ? 32 : 16;   // bytes of one 8-element piece
+  const bool vec = g.K % 8 == 0 && (reinterpret_cast<uintptr_t>(g.a) % al) == 0 && (reinterpret_cast<uintptr_t>(g.w) % al) == 0 &&
+                   (g.lda * esz) % al == 0 && (g.sa * esz) % al == 0 && (g.sw * esz) % al == 0;
+  const dim3 grid((g.N + 7) / 8, g.items);
+  if (dtype == B200_F32) {
+    if (vec) B200_CUDA(launch_pdl(small_gemv_kernel<float, true>, grid, dim3(256), 0, st, stack_pdl(), g));
+    else B200_CUDA(launch_pdl(small_gemv_kernel<float, false>, grid, dim3(256), 0, st, stack_pdl(), g));
+  } else {
+    if (vec) B200_CUDA(launch_pdl(small_gemv_kernel<__nv_bfloat16, true>, grid, dim3(256), 0, st, stack_pdl(), g));
+    else B200_CUDA(launch_pdl(small_gemv_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, st, stack_pdl(), g));
+  }
+  return B200_OK;
+}
+
 int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
   const int r = p.l.kv_rank, dr = p.l.rot_dim, H = p.a.heads, dn = p.a.dim, kd = r + dr;
@@ -480,16 +685,49 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
   if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(latent_prep_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   const size_t esz = dtype == B200_F32 ? 4 : 2;
-  StackGemm g;   // folded query of head h = uk_hᵀ · q_plain of head h
-  g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.k1 = dn; g.sa = dn + dr;
-  g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
-  g.M = p.n_tok; g.N = r; g.K = dn; g.batch = H;
-  g.epi = SEPI_STORE; g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;
-  if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
-  const size_t smem = (size_t)(kd + 4 * (2 + r)) * 4;
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
-  else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
-  StackGemm v;   // head h's output = uv_h · (softmax-weighted latent of head h)
+  const bool small = p.n_tok <= kSmallRows;
+  // folded query of head h = uk_hᵀ · q_plain of head h
+  if (small) {
+    SmallGemv g;
+    g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.sa = dn + dr;
+    g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
+    g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;
+    g.M = p.n_tok; g.N = r; g.K = dn; g.items = H;
+    if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
+  } else {
+    StackGemm g;
+    g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.k1 = dn; g.sa = dn + dr;
+    g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
+    g.M = p.n_tok; g.N = r; g.K = dn; g.batch = H;
+    g.epi = SEPI_STORE; g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;
+    if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
+  }
+  const size_t split_smem = (size_t)(H + 32) * kd * 4;
+  if (small && p.split_ws != nullptr && p.nsplit >= 1 && H <= 8 * kLatHeadsPerWarp && split_smem <= 200 * 1024) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      B200_CUDA(cudaFuncSetAttribute(latent_attn_split_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      B200_CUDA(cudaFuncSetAttribute(latent_attn_split_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr_done = true;
+    }
+    const dim3 grid(p.n_tok, p.nsplit);
+    if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_split_kernel<float>, grid, dim3(256), split_smem, st, stack_pdl(), p));
+    else B200_CUDA(launch_pdl(latent_attn_split_kernel<__nv_bfloat16>, grid, dim3(256), split_smem, st, stack_pdl(), p));
+  } else {
+    const size_t smem = (size_t)(kd + 4 * (2 + r)) * 4;
+    if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
+    else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
+  }
+  // head h's output = uv_h · (softmax-weighted latent of head h)
+  if (small) {
+    SmallGemv v;
+    v.a = p.ol; v.lda = (int64_t)H * r; v.sa = r;
+    v.w = p.l.uv; v.sw = (int64_t)p.a.vdim * r;
+    v.c = p.out; v.ldc = p.ld_out; v.sc = p.a.vdim;
+    v.M = p.n_tok; v.N = p.a.vdim; v.K = r; v.items = H;
+    return launch_small_gemv(v, dtype, st);
+  }
+  StackGemm v;
   v.a = p.ol; v.lda = (int64_t)H * r; v.k1 = r; v.sa = r;
   v.w = p.l.uv; v.sw = (int64_t)p.a.vdim * r;
   v.M = p.n_tok; v.N = p.a.vdim; v.K = r; v.batch = H;
@@ -503,8 +741,17 @@ int run_mlstm(const MlstmRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(p.a.heads > 0 && p.a.dim > 0 && p.a.vdim > 0 && p.gate_cap > 0.f, "mlstm: bad sizes");
   B200_CHECK_ARG(p.a.dim <= kMlstmMaxDim, "mlstm: key size above %d not built", kMlstmMaxDim);
   const dim3 grid(p.n_seg, p.a.heads, (p.a.vdim + 1 + 7) / 8);
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(mlstm_scan_kernel<float>, grid, dim3(256), 0, st, stack_pdl(), p));
-  else B200_CUDA(launch_pdl(mlstm_scan_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, stack_pdl(), p));
+#define B200_SCAN(DR)                                                                                              \
+  do {                                                                                                             \
+    if (dtype == B200_F32) B200_CUDA(launch_pdl(mlstm_scan_kernel<float, DR>, grid, dim3(256), 0, st, stack_pdl(), p)); \
+    else B200_CUDA(launch_pdl(mlstm_scan_kernel<__nv_bfloat16, DR>, grid, dim3(256), 0, st, stack_pdl(), p));     \
+  } while (0)
+  if (p.a.dim <= 32) B200_SCAN(1);
+  else if (p.a.dim <= 64) B200_SCAN(2);
+  else if (p.a.dim <= 128) B200_SCAN(4);
+  else if (p.a.dim <= 256) B200_SCAN(8);
+  else B200_SCAN(16);
+#undef B200_SCAN
   if (p.mid == nullptr) return B200_OK;
   B200_CHECK_ARG(p.head_norm != nullptr, "mlstm: null head norm");
   const dim3 og((p.n_tok * p.a.heads + 3) / 4);
@@ -524,6 +771,26 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(m.experts <= 8192, "moe: more than 8192 experts not built");
   const int P = p.n_tok * m.top, n_tiles = moe_tiles(P, m.experts), E = m.experts;
   int rc;
+  if (p.small) {   // a few tokens: router, then every (token, choice) pair is an item of a small product with its expert
+    B200_CHECK_ARG(p.n_tok <= kSmallRows, "moe: the small path takes up to %d tokens", kSmallRows);
+    SmallGemv rz;
+    rz.a = p.h; rz.lda = p.width; rz.w = m.router; rz.c = p.z; rz.ldc = E; rz.c_f32 = true;
+    rz.M = p.n_tok; rz.N = E; rz.K = p.width; rz.items = 1;
+    if ((rc = launch_small_gemv(rz, dtype, st)) != B200_OK) return rc;
+    B200_CUDA(launch_pdl(moe_route_kernel, dim3((p.n_tok + 3) / 4), dim3(128), 0, st, stack_pdl(), p));
+    if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+    else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+    SmallGemv g;
+    g.a = p.a_perm; g.sa = p.width; g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width; g.item_mat = p.sel_e;
+    g.c = p.gu; g.sc = 2 * m.expert_ff; g.M = 1; g.N = 2 * m.expert_ff; g.K = p.width; g.items = P;
+    if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
+    if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, 2 * m.expert_ff, P, m.expert_ff, m.limit, dtype, st)) != B200_OK)
+      return rc;
+    SmallGemv d;
+    d.a = p.act; d.sa = m.expert_ff; d.w = m.w_exp_out; d.sw = (int64_t)p.width * m.expert_ff; d.item_mat = p.sel_e;
+    d.c = p.outp; d.sc = p.width; d.c_f32 = true; d.M = 1; d.N = p.width; d.K = m.expert_ff; d.items = P;
+    if ((rc = launch_small_gemv(d, dtype, st)) != B200_OK) return rc;
+  } else {
   StackGemm rz;   // router logits in fp32
   rz.a = p.h; rz.lda = p.width; rz.k1 = p.width;
   rz.w = m.router; rz.M = p.n_tok; rz.N = E; rz.K = p.width;
@@ -549,6 +816,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   d.epi = SEPI_STORE_F32; d.c = p.outp; d.ldc = p.width;
   d.tile_group = g.tile_group; d.tile_row0 = g.tile_row0; d.group_end = g.group_end; d.n_tiles = n_tiles;
   if ((rc = launch_stack_gemm(d, dtype, st)) != B200_OK) return rc;
+  }
   if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   return B200_OK;

@@ -18,6 +18,25 @@ int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu,
 // logits (fp32) and their bf16 copy <- cap·tanh(logits / cap)
 int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total, float cap, cudaStream_t st);
 
+// ---- small products of decode-shaped steps: `items` independent products of up to 8 rows each, one warp per output row.
+// Item z multiplies rows a + m·lda + z·sa (m < M) with matrix w + (item_mat ? item_mat[z] : z)·sw ([N, K] row-major) into
+// c + m·ldc + z·sc (T, or fp32 when c_f32).  Serves the per-head folds of latent attention, router and gate logits, and
+// the chosen experts of a few tokens (item = (token, choice) pair, matrix = that pair's expert).
+constexpr int kSmallRows = 8;
+struct SmallGemv {
+  const void* a = nullptr;
+  int64_t lda = 0, sa = 0;
+  const void* w = nullptr;
+  int64_t sw = 0;
+  const int32_t* item_mat = nullptr;
+  const float* bias = nullptr;   // [N], shared by the items
+  void* c = nullptr;
+  int64_t ldc = 0, sc = 0;
+  bool c_f32 = false;
+  int M = 1, N = 0, K = 0, items = 1;
+};
+int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st);
+
 // ---- latent attention: everything between the in-projection and the out-projection
 constexpr int kLatentMaxRank = 512;
 struct LatentRun {
@@ -36,12 +55,15 @@ struct LatentRun {
   void* ol = nullptr;            // [n_tok, heads·kv_rank] T: softmax-weighted latents
   void* out = nullptr;           // [n_tok, ld_out] T: head h at columns h·vdim
   int64_t ld_out = 0;
-  // decode-shaped steps (few rows, long key lists): keys split over CTAs, partial softmaxes merged by the CTA that
-  // finishes last (ticket)
+  // decode-shaped steps (up to kSmallRows rows, long key lists): one CTA per (row, split of the key list) serves ALL heads
+  // from key rows staged once in shared memory; the partial softmaxes [row][head][split][2 + kv_rank] in split_ws are
+  // merged by the CTA that finishes a row last (split_tickets [row], zero-initialised, self-resetting)
   float* split_ws = nullptr;
   unsigned int* split_tickets = nullptr;
-  int nsplit = 1, keys_per_split = 0;
+  int nsplit = 0, keys_per_split = 0;
 };
+constexpr int kLatentMaxSplits = 32;
+constexpr int kLatentSplitKeys = 128;
 int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st);
 
 // ---- mLSTM: recurrence + head norm + output gate
@@ -89,6 +111,9 @@ struct MoeRun {
   bool shared_f32 = false;
   const void* sg = nullptr;      // T: the shared gate's logit of token t at sg[t·ld_sg]
   int64_t ld_sg = 0;
+  // steps of up to kSmallRows tokens: no sorting — every (token, choice) pair is an item of a small product with its
+  // expert's matrices
+  bool small = false;
 };
 __host__ __device__ inline int moe_tiles(int pairs, int experts) { return (pairs + 63) / 64 + experts; }
 inline int64_t moe_plan_ints(int pairs, int experts) { return 2 * (int64_t)experts + 2 * moe_tiles(pairs, experts); }

@@ -70,6 +70,108 @@ def device_stack_weights(spec: models.StackSpec, device, seed: int = 0) -> Dict[
     return w
 
 
+# Silatar sizes: four layers [mLSTM + dense, latent attention + experts, latent attention + dense, mLSTM + experts], the
+# middle two run twice (six runs).  The Kozusun model beside it has the same width, vocabulary and number of runs, full
+# causal attention of 128-wide heads, and a gated feed-forward of two thirds the dense width (equal parameters).
+SILATAR_SIZES = {
+    "s2048": dict(width=2048, vocab=65536, heads=16, dim=64, rot_dim=64, vdim=128, kv_rank=512, rec_heads=8, rec_dim=128,
+                  rec_vdim=256, ff=8192, experts=32, top=4, expert_ff=1024, shared_ff=1024, koz_heads=16, koz_kv=8, koz_ff=5464),
+    "s3072": dict(width=3072, vocab=65536, heads=24, dim=64, rot_dim=64, vdim=128, kv_rank=512, rec_heads=8, rec_dim=192,
+                  rec_vdim=384, ff=12288, experts=32, top=4, expert_ff=1536, shared_ff=1536, koz_heads=24, koz_kv=8, koz_ff=8192),
+}
+
+
+def silatar_spec(name: str, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = SILATAR_SIZES[name]
+    rot = models.RotarySpec(dims=z["rot_dim"], base=5e5, factor=4.0, original=2048, fast=32.0, slow=1.0)
+    lat = models.LatentSpec(z["heads"], z["dim"], z["rot_dim"], z["vdim"], z["kv_rank"], (z["dim"] + z["rot_dim"]) ** -0.5, rot)
+    rec = models.MlstmSpec(z["rec_heads"], z["rec_dim"], z["rec_vdim"], 15.0)
+    moe = models.MoeSpec(z["experts"], z["top"], z["expert_ff"], 7.0, z["shared_ff"], 7.0)
+    L = models.StackLayerSpec
+    layers = (L(mixer="mlstm", mlstm=rec, ff_kind="dense", ff=z["ff"], ff_act="gelu_erf"),
+              L(mixer="latent_attention", latent=lat, ff_kind="moe", moe=moe),
+              L(mixer="latent_attention", latent=lat, ff_kind="dense", ff=z["ff"], ff_act="gelu_erf"),
+              L(mixer="mlstm", mlstm=rec, ff_kind="moe", moe=moe))
+    return models.StackSpec(name="silatar-" + name, architecture="Silatar", width=z["width"], vocab=z["vocab"], layers=layers,
+                            loop_start=1, loop_stop=3, loop_times=2, norm_eps=1e-5, block="sandwich", norm_kind="layer",
+                            loop_mix=False, logit_softcap=30.0, max_ctx=max_ctx, max_slots=max_slots)
+
+
+def kozusun_beside(name: str, n_runs: int, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = SILATAR_SIZES[name]
+    attn = models.AttnSpec(z["koz_heads"], z["koz_kv"], 128, 128, 128 ** -0.5, 0, 0)
+    return models.StackSpec(name="kozusun-" + name, architecture="Kozusun", width=z["width"], vocab=z["vocab"],
+                            layers=tuple(models.StackLayerSpec(attn, z["koz_ff"]) for _ in range(n_runs)), embed_scale=8.0,
+                            residual_mult=0.3, norm_eps=1e-5, norm_offset=1.0, side_dim=0, max_ctx=max_ctx, max_slots=max_slots)
+
+
+def device_silatar_weights(spec: models.StackSpec, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random Silatar weights straight in the engine's layout on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = spec.width
+
+    def mat(*shape):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * (shape[-1] ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, centre=1.0):
+        return centre + torch.randn(n, generator=g, device=device, dtype=torch.float32) * 0.05
+
+    w = {"embed": mat(spec.vocab, W), "head": mat(spec.vocab, W), "final_norm": vec(W)}
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w[p + "norm"], w[p + "post_norm"], w[p + "ff_norm"], w[p + "ff_post_norm"] = vec(W), vec(W), vec(W), vec(W)
+        w[p + "w_in"], w[p + "b_in"], w[p + "w_out"] = mat(lay.n_in, W), vec(lay.n_in, 0.0), mat(W, lay.k_out)
+        if L.mixer == "latent_attention":
+            a = L.latent
+            w[p + "c_norm"], w[p + "uk_t"], w[p + "uv"] = vec(a.kv_rank), mat(a.heads, a.kv_rank, a.dim), mat(a.heads * a.vdim, a.kv_rank)
+        else:
+            w[p + "head_norm"] = vec(L.mlstm.heads * L.mlstm.vdim)
+            w[p + "b_in"][lay.off_gate + L.mlstm.heads:lay.off_gate + 2 * L.mlstm.heads] += 3.0   # a memory that keeps
+        if L.ff_kind == "moe":
+            m = L.moe
+            w[p + "router"] = mat(m.experts, W)
+            w[p + "w_exp_in"], w[p + "w_exp_out"] = mat(m.experts, 2 * m.expert_ff, W), mat(m.experts, W, m.expert_ff)
+            if m.shared_ff > 0:
+                w[p + "w_ff_in"], w[p + "w_ff_out"] = mat((2 * m.shared_ff + 1 + 7) // 8 * 8, W), mat(W, m.shared_ff)
+        else:
+            w[p + "w_ff_in"], w[p + "w_ff_out"] = mat(L.ff, W), mat(W, L.ff)
+    return w
+
+
+def compare_silatar(sizes: List[str], steps: int = 5, warmup: int = 3, prompt_len: int = 2048, n_decode: int = 32) -> dict:
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    timer = _Timer(dev)
+    max_ctx = prompt_len + n_decode + 8
+    rows = {}
+    for name in sizes:
+        sspec = silatar_spec(name, max_ctx)
+        eng = engine.DecodeEngine(sspec, device_silatar_weights(sspec, dev))
+        k = _measure(eng, True, prompt_len, n_decode, timer, steps, warmup, sspec.vocab)
+        k["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+        k["launches_per_decode_token"] = eng.launches_per_token
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        kspec = kozusun_beside(name, len(sspec.runs()), max_ctx)
+        eng = engine.DecodeEngine(kspec, device_stack_weights(kspec, dev))
+        l = _measure(eng, True, prompt_len, n_decode, timer, steps, warmup, kspec.vocab)
+        l["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+        l["launches_per_decode_token"] = eng.launches_per_token
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+        rows[name] = {"silatar": k, "kozusun": l, "ratio": {m: round(k[m] / l[m], 3) for m in k if m.endswith("tok_s")}}
+    return {"metric": "silatar_compare", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+            "decode_steps": n_decode, "steps": steps, "warmup": warmup, "l2": "flushed between timed iterations",
+            "sizes": rows}
+
+
+def main_silatar(sizes: str, steps: int, warmup: int) -> None:
+    names = [s for s in sizes.split(",") if s] if sizes and sizes != "all" else list(SILATAR_SIZES)
+    print(json.dumps(compare_silatar(names, steps=steps, warmup=warmup)), flush=True)
+
+
 class _Timer:
     def __init__(self, device):
         self.device = device
