@@ -326,6 +326,7 @@ typedef struct b200_latent_desc {
   int32_t kv_rank, rot_dim, rot_dims;
   const float* c_norm;      /* [kv_rank] */
   const void* uk_t;         /* [heads][kv_rank][dim]: uk of head h transposed */
+  const void* uk;           /* [heads·dim][kv_rank] as stored, or NULL (then prompts take the general kernels) */
   const void* uv;           /* [heads·vdim][kv_rank] */
   const float* rot_table;   /* [max_ctx][rot_dims/2][2] fp32 */
 } b200_latent_desc;

@@ -410,10 +410,14 @@ def test_the_constants_matter():
 
 
 def test_bf16_paths_agree_with_each_other():
-    """Widths the fast paths take (multiples of 8, 32 and more rows for the tensor-core products, up to 8 rows for the
-    weight-streaming ones): the same prompt whole, in portions, token by token and beside other requests."""
-    cfg = config([(latent(heads=4, dim=16, rot_dim=8, vdim=16, kv_rank=64), moe(experts=8, top=2, ff=32, shared=(64, 2.0))),
-                  (mlstm(heads=2, dim=32, vdim=32), dense(128))], width=128, vocab=160, loop=(0, 2, 2))
+    """Sizes the fast paths take (multiples of 8; 32 and more rows for the tensor-core products and the per-expert products,
+    16 and more rows of a sequence with dim + rot_dim == vdim == 64 for the tensor-core prompt attention over expanded keys,
+    up to 8 rows for the weight-streaming products and the split-key decode attention): the same prompt whole, in portions,
+    token by token and beside other requests."""
+    cfg = config([(latent(heads=2, dim=32, rot_dim=32, vdim=64, kv_rank=64, rot=dict(ROT, dims=32)),
+                   moe(experts=8, top=2, ff=64, shared=(64, 2.0))),
+                  (mlstm(heads=2, dim=32, vdim=32), dense(128)),
+                  (latent(heads=4, dim=16, rot_dim=8, vdim=16, kv_rank=64), dense(64))], width=128, vocab=160, loop=(0, 2, 2))
     eng, w = make(cfg, torch.bfloat16, max_ctx=256)
     toks = tokens(100, cfg["vocab"], 90)
     whole = eng.step([(0, toks, list(range(100)))])

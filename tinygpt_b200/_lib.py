@@ -42,7 +42,8 @@ class AttnDesc(C.Structure):
 
 class LatentDesc(C.Structure):
     _fields_ = [("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
-                ("c_norm", C.c_void_p), ("uk_t", C.c_void_p), ("uv", C.c_void_p), ("rot_table", C.c_void_p)]
+                ("c_norm", C.c_void_p), ("uk_t", C.c_void_p), ("uk", C.c_void_p), ("uv", C.c_void_p),
+                ("rot_table", C.c_void_p)]
 
 
 class MlstmDesc(C.Structure):

@@ -245,6 +245,9 @@ int b200_stack_mlstm(float* out, const void* proj, int64_t ld_proj, int64_t off_
   p.state = state; p.slot_stride = slot_stride;
   p.seg_row0 = row0; p.seg_count = count; p.slot = slot; p.pos = pos; p.n_seg = (int)n_seq; p.n_tok = (int)n_rows;
   p.o = out;
+  Scratch sc;
+  p.gab = (float*)sc.take((size_t)n_rows * sizes->heads * 3 * 4);
+  B200_CHECK_ARG(p.gab, "stack_mlstm: out of device memory");
   return b200::run_mlstm(p, dtype, (cudaStream_t)stream);
 }
 

@@ -108,12 +108,12 @@ struct StackEngine {
   size_t s_slot = 0;               // floats per slot
   bool recurrent = false;          // some run carries state that cannot be rewound
   void *qa = nullptr, *ol = nullptr, *lin_tmp = nullptr;
-  float *projf = nullptr, *rec_o = nullptr, *y2 = nullptr;
+  float *projf = nullptr, *rec_o = nullptr, *rec_ab = nullptr, *y2 = nullptr;
   int32_t *m_seg_row0 = nullptr, *m_seg_count = nullptr;
   MoeRun moe_ws{};                 // the routing workspace's pointers
   float* lat_ws = nullptr;         // split-key partials of decode-shaped latent attention
-  unsigned int* lat_tickets = nullptr;
-  int lat_heads_max = 0, lat_rank_max = 0;
+  int lat_heads_max = 0, lat_rank_max = 0, lat_hd_max = 0, lat_hv_max = 0;
+  __nv_bfloat16 *lat_c = nullptr, *lat_kp = nullptr, *lat_k = nullptr, *lat_v = nullptr, *lat_q = nullptr;   // one sequence's expanded keys / values
   int qa_max = 0, ol_max = 0, rec_o_max = 0, moe_e_max = 0, moe_top_max = 0, moe_ff_max = 0, lin_max = 0;
   bool any_rec = false, any_moe = false;
   struct SPlans {
@@ -202,16 +202,26 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_lt = take(sw ? T * s->lin_max * 2 : 0);
   const size_t o_pf = take(s->any_rec ? (size_t)kMaxBatch * s->n_in_max * 4 + T * 2 * s->max_heads * 4 : 0);
   const size_t o_ro = take(s->any_rec ? T * s->rec_o_max * 4 : 0), o_y2 = take(sw ? T * W * 4 : 0);
+  const size_t o_rab = take(s->any_rec ? T * 3 * s->max_heads * 4 : 0);
   const size_t P = T * std::max(1, s->moe_top_max);
   const size_t o_mz = take(s->any_moe ? T * s->moe_e_max * 4 : 0), o_me = take(s->any_moe ? P * 4 : 0);
   const size_t o_mw = take(s->any_moe ? P * 4 : 0), o_mp = take(s->any_moe ? (size_t)moe_plan_ints((int)P, s->moe_e_max) * 4 : 0);
   const size_t o_ms = take(s->any_moe ? P * 4 : 0), o_ma = take(s->any_moe ? P * W * s->esz : 0);
   const size_t o_mg = take(s->any_moe ? P * 2 * s->moe_ff_max * s->esz : 0), o_mc = take(s->any_moe ? P * s->moe_ff_max * s->esz : 0);
-  const size_t o_mo = take(s->any_moe ? P * W * 4 : 0);
+  const size_t o_mo = take(s->any_moe ? P * W * 4 : 0), o_mb = take(s->any_moe && s->fast ? P * W * 2 : 0);
   const size_t o_lw = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * s->lat_heads_max * kLatentMaxSplits * (2 + s->lat_rank_max) * 4 : 0);
-  const size_t o_lt2 = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * 4 : 0);
+  const bool lx = s->fast && s->lat_rank_max > 0;
+  const size_t C = d.max_ctx;
+  const size_t o_lc = take(lx ? C * s->lat_rank_max * 2 : 0), o_lkp = take(lx ? C * s->lat_hd_max * 2 : 0);
+  const size_t o_lk = take(lx ? C * s->lat_hd_max * 2 : 0), o_lv = take(lx ? C * s->lat_hv_max * 2 : 0);
+  const size_t o_lq = take(lx ? T * s->lat_hd_max * 2 : 0);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
+  s->lat_c = lx ? (__nv_bfloat16*)(s->ws + o_lc) : nullptr;
+  s->lat_kp = (__nv_bfloat16*)(s->ws + o_lkp);
+  s->lat_k = lx ? (__nv_bfloat16*)(s->ws + o_lk) : nullptr;
+  s->lat_v = (__nv_bfloat16*)(s->ws + o_lv);
+  s->lat_q = (__nv_bfloat16*)(s->ws + o_lq);
   s->ws_tok = tok;
   s->ws_rows = rows;
   s->x = (float*)(s->ws + o_x);
@@ -237,6 +247,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->lin_tmp = s->ws + o_lt;
   s->projf = (float*)(s->ws + o_pf);
   s->rec_o = (float*)(s->ws + o_ro);
+  s->rec_ab = (float*)(s->ws + o_rab);
   s->y2 = (float*)(s->ws + o_y2);
   s->moe_ws.z = (float*)(s->ws + o_mz);
   s->moe_ws.sel_e = (int32_t*)(s->ws + o_me);
@@ -247,8 +258,8 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->moe_ws.gu = s->ws + o_mg;
   s->moe_ws.act = s->ws + o_mc;
   s->moe_ws.outp = (float*)(s->ws + o_mo);
+  s->moe_ws.outp_bf = (__nv_bfloat16*)(s->ws + o_mb);
   s->lat_ws = s->lat_rank_max > 0 ? (float*)(s->ws + o_lw) : nullptr;
-  s->lat_tickets = (unsigned int*)(s->ws + o_lt2);
   s->cat = (__nv_bfloat16*)(s->ws + o_cat);
   s->attn_ws = (float*)(s->ws + o_aws);
   s->attn_tickets = (unsigned int*)(s->ws + o_tick);
@@ -547,11 +558,51 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     a.qa = s->qa; a.ol = s->ol; a.out = s->mid; a.ld_out = L.k_out;
     if (n_tok <= kSmallRows && s->lat_ws != nullptr) {   // splits follow the context the engine was built for, not the
       a.split_ws = s->lat_ws;                             // positions of the moment: a captured step stays valid
-      a.split_tickets = s->lat_tickets;
       a.nsplit = std::min(kLatentMaxSplits, (d.max_ctx + kLatentSplitKeys - 1) / kLatentSplitKeys);
       a.keys_per_split = ((d.max_ctx + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
     }
-    if ((rc = run_latent_attention(a, dt, st)) != B200_OK) return rc;
+    // prompts of bf16 engines whose heads suit the tensor-core attention kernel: per sequence, keys and values are expanded
+    // from the cache rows by two tcgen05 products and laid out per head; what is left takes the general kernels
+    const int hd = L.attn.dim + L.lat.rot_dim, Hh = L.attn.heads, rk = L.lat.kv_rank;
+    bool tc = s->fast && s->lat_k != nullptr && L.lat.uk != nullptr && hd == L.attn.vdim && (hd == 64 || hd == 128) &&
+              gemm_shape_ok(Hh * L.attn.dim, rk) && gemm_shape_ok(Hh * hd, rk) && L.k_out % 8 == 0 && L.n_in % 8 == 0;
+    bool any = false;
+    for (const StackEngine::Seg& g : s->segs) any = any || g.count >= kTcRows;
+    if (!tc || !any) {
+      if ((rc = run_latent_attention(a, dt, st)) != B200_OK) return rc;
+    } else {
+      if ((rc = launch_latent_prep(a, dt, st)) != B200_OK) return rc;
+      const __nv_bfloat16* P0 = (const __nv_bfloat16*)s->proj;
+      for (const StackEngine::Seg& g : s->segs) {
+        if (g.count < kTcRows) {   // a short part: the general kernels on its rows (the cache rows are written again, equal)
+          LatentRun b = a;
+          b.proj = P0 + (size_t)g.row0 * L.n_in;
+          b.slot = a.slot + g.row0; b.pos = a.pos + g.row0; b.n_tok = g.count;
+          b.qa = (__nv_bfloat16*)s->qa + (size_t)g.row0 * Hh * (rk + L.lat.rot_dim);
+          b.ol = (__nv_bfloat16*)s->ol + (size_t)g.row0 * Hh * rk;
+          b.out = (__nv_bfloat16*)s->mid + (size_t)g.row0 * L.k_out;
+          b.split_ws = nullptr;
+          if ((rc = run_latent_attention(b, dt, st)) != B200_OK) return rc;
+          continue;
+        }
+        const int ctx = g.pos0 + g.count, kd = rk + L.lat.rot_dim;
+        const __nv_bfloat16* rows = (const __nv_bfloat16*)a.cache + (size_t)g.slot * a.slot_stride;
+        B200_CUDA(cudaMemcpy2DAsync(s->lat_c, (size_t)rk * 2, rows, (size_t)kd * 2, (size_t)rk * 2, (size_t)ctx,
+                                    cudaMemcpyDeviceToDevice, st));
+        if ((rc = launch_gemm_bf16(s->lat_kp, s->lat_c, L.lat.uk, ctx, Hh * L.attn.dim, rk, st)) != B200_OK) return rc;
+        if ((rc = launch_gemm_bf16(s->lat_v, s->lat_c, L.lat.uv, ctx, Hh * L.attn.vdim, rk, st)) != B200_OK) return rc;
+        LatentPack k;
+        k.a = L.attn; k.l = L.lat; k.kp = s->lat_kp; k.cache_rows = rows;
+        k.proj = P0 + (size_t)g.row0 * L.n_in; k.ld_proj = L.n_in; k.off_q = L.off_q;
+        k.qa = (const __nv_bfloat16*)s->qa + (size_t)g.row0 * Hh * kd;
+        k.kbuf = s->lat_k; k.qbuf = s->lat_q; k.ctx = ctx; k.count = g.count;
+        if ((rc = launch_latent_pack(k, st)) != B200_OK) return rc;
+        if ((rc = launch_attn_prefill_window((__nv_bfloat16*)s->mid + (size_t)g.row0 * L.k_out, L.k_out, s->lat_q, nullptr,
+                                             (int64_t)Hh * hd, s->lat_k, s->lat_v, g.count, Hh, Hh, hd, g.pos0, L.attn.scale, 0, 0,
+                                             st)) != B200_OK)
+          return rc;
+      }
+    }
   } else {
     const int H = L.attn.heads;
     MlstmRun m;
@@ -567,12 +618,9 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
         g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
         g.c = gates; g.ldc = 2 * H; g.c_f32 = true; g.M = n_tok; g.N = 2 * H; g.K = W; g.items = 1;
         if ((rc = launch_small_gemv(g, dt, st)) != B200_OK) return rc;
-      } else {
-      StackGemm g;
-      g.a = s->h; g.lda = W; g.k1 = W;
-      g.w = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz; g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
-      g.M = n_tok; g.N = 2 * H; g.K = W; g.epi = SEPI_STORE_F32; g.c = gates; g.ldc = 2 * H;
-      if ((rc = launch_stack_gemm(g, dt, st)) != B200_OK) return rc;
+      } else if ((rc = launch_skinny_f32(gates, s->h, (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz,
+                                         L.b_in ? L.b_in + L.off_gate : nullptr, n_tok, 2 * H, W, dt, st)) != B200_OK) {
+        return rc;
       }
       m.gates = gates; m.ld_gates = 2 * H;
     }
@@ -583,7 +631,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     } else {
       m.n_seg = (int)s->segs.size(); m.seg_row0 = s->m_seg_row0; m.seg_count = s->m_seg_count;
     }
-    m.o = s->rec_o; m.head_norm = L.rec.head_norm; m.mid = s->mid; m.ld_mid = L.k_out;
+    m.gab = s->rec_ab; m.o = s->rec_o; m.head_norm = L.rec.head_norm; m.mid = s->mid; m.ld_mid = L.k_out;
     if ((rc = run_mlstm(m, dt, st)) != B200_OK) return rc;
   }
   if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x, st)) != B200_OK)
@@ -601,6 +649,12 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   MoeRun m = s->moe_ws;
   m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
   m.small = n_tok <= kSmallRows;
+  m.tc = s->fast && n_tok >= kGemmRows && gemm_shape_ok(2 * L.moe.expert_ff, W) && gemm_shape_ok(W, L.moe.expert_ff);
+  if (m.tc) {   // that path reads the group sizes back: not inside a stream capture
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    B200_CUDA(cudaStreamIsCapturing(st, &cs));
+    m.tc = cs == cudaStreamCaptureStatusNone;
+  }
   if (L.moe.shared_ff > 0) {
     const int fs = L.moe.shared_ff, n_sh = up8i(2 * fs + 1);
     if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, n_sh, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
@@ -1028,6 +1082,8 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       s->ol_max = std::max(s->ol_max, a.heads * q.kv_rank);
       s->lat_heads_max = std::max(s->lat_heads_max, a.heads);
       s->lat_rank_max = std::max(s->lat_rank_max, q.kv_rank);
+      s->lat_hd_max = std::max(s->lat_hd_max, a.heads * (a.dim + q.rot_dim));
+      s->lat_hv_max = std::max(s->lat_hv_max, a.heads * a.vdim);
     } else {
       B200_CHECK_ARG(a.dim <= kMlstmMaxDim && L.rec.gate_cap > 0.f && L.rec.head_norm, "engine_create_stack: layer %d: mLSTM description", l);
       B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.heads * a.dim <= L.n_in &&

@@ -3,6 +3,10 @@
 // Every kernel starts with griddepcontrol.launch_dependents + griddepcontrol.wait (programmatic dependent launch).
 #include "stack_mix.cuh"
 
+#include <vector>
+
+#include "ops.cuh"
+
 namespace b200 {
 
 namespace {
@@ -201,6 +205,32 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
   }
 }
 
+// Per-head key and query rows for the tensor-core prompt attention (see LatentPack): one CTA per key row, then per query row.
+__global__ void __launch_bounds__(128) latent_pack_kernel(const LatentPack p) {
+  pdl_trigger();
+  pdl_wait();
+  const int H = p.a.heads, dn = p.a.dim, dr = p.l.rot_dim, r = p.l.kv_rank, hd = dn + dr, kd = r + dr;
+  const int row = blockIdx.x;
+  if (row < p.ctx) {
+    const __nv_bfloat16* kp = p.kp + (int64_t)row * H * dn;
+    const __nv_bfloat16* rot = p.cache_rows + (int64_t)row * kd + r;
+    __nv_bfloat16* dst = p.kbuf + (int64_t)row * H * hd;
+    for (int i = threadIdx.x; i < H * hd; i += blockDim.x) {
+      const int h = i / hd, e = i % hd;
+      dst[i] = e < dn ? kp[h * dn + e] : rot[e - dn];
+    }
+  } else {
+    const int t = row - p.ctx;
+    const __nv_bfloat16* q = p.proj + (int64_t)t * p.ld_proj + p.off_q;
+    const __nv_bfloat16* qa = p.qa + (int64_t)t * H * kd;
+    __nv_bfloat16* dst = p.qbuf + (int64_t)t * H * hd;
+    for (int i = threadIdx.x; i < H * hd; i += blockDim.x) {
+      const int h = i / hd, e = i % hd;
+      dst[i] = e < dn ? q[h * hd + e] : qa[h * kd + r + (e - dn)];
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------- small products
 template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
 template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
@@ -222,6 +252,7 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
   const int64_t mat = g.item_mat != nullptr ? g.item_mat[z] : z;
   const T* wr = static_cast<const T*>(g.w) + mat * g.sw + (int64_t)n * g.K;
   const T* a = static_cast<const T*>(g.a) + (int64_t)z * g.sa;
+  const int M = g.m_total > 0 ? min(g.M, g.m_total - z * g.M) : g.M;
   float acc[kSmallRows];
 #pragma unroll
   for (int m = 0; m < kSmallRows; ++m) acc[m] = 0.f;
@@ -231,7 +262,7 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
       load8<T>(wr + k, wv);
 #pragma unroll
       for (int m = 0; m < kSmallRows; ++m) {
-        if (m < g.M) {
+        if (m < M) {
           float av[8];
           load8<T>(a + (int64_t)m * g.lda + k, av);
 #pragma unroll
@@ -244,16 +275,17 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
       const float wv = ldf<T>(wr + k);
 #pragma unroll
       for (int m = 0; m < kSmallRows; ++m)
-        if (m < g.M) acc[m] = fmaf(wv, ldf<T>(a + (int64_t)m * g.lda + k), acc[m]);
+        if (m < M) acc[m] = fmaf(wv, ldf<T>(a + (int64_t)m * g.lda + k), acc[m]);
     }
   }
 #pragma unroll
   for (int m = 0; m < kSmallRows; ++m) {
-    if (m >= g.M) break;
+    if (m >= M) break;
     float v = warp_sum(acc[m]);
     if (lane == 0) {
       if (g.bias != nullptr) v += g.bias[n];
-      const int64_t o = (int64_t)m * g.ldc + (int64_t)z * g.sc + n;
+      if (g.bias_m != nullptr) v += g.bias_m[z * g.M + m];
+      const int64_t o = (int64_t)m * g.ldc + (int64_t)z * g.sc + (int64_t)n * g.nc;
       if (g.c_f32) static_cast<float*>(g.c)[o] = v;
       else static_cast<T*>(g.c)[o] = cvt<T>(v);
     }
@@ -264,15 +296,13 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
 // One CTA of eight warps per (row, split of the key list).  The split's key rows [c | rotated key part] are staged in
 // shared memory 32 at a time and serve ALL heads (warp w takes heads w, w + 8, …): the rows are read from memory once per
 // row of the step instead of once per head.  Per head and chunk: 32 scores (every key's dot product by the whole warp),
-// the online softmax, the weighted latents.  Partials go to split_ws; the CTA that takes a row's last ticket merges
-// the splits of every head (non-blocking: nobody waits for anybody).
+// the online softmax, the weighted latents.  Partials go to split_ws; latent_merge_kernel joins the splits.
 constexpr int kLatHeadsPerWarp = 4;   // heads <= 32
 template <typename T>
 __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun p) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float sm[];
-  __shared__ unsigned int s_ticket;
   const int t = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = p.l.kv_rank, kd = r + p.l.rot_dim, H = p.a.heads;
   float* q = sm;                          // [H][kd], scaled
@@ -281,6 +311,7 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
   for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
   const int n_keys = p.pos[t] + 1;
   const int k_lo = split * p.keys_per_split, k_hi = min(n_keys, k_lo + p.keys_per_split);
+  if (k_lo >= n_keys) return;   // the merge reads the splits that saw a key, and only those
   const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
   float m[kLatHeadsPerWarp], sum[kLatHeadsPerWarp], acc[kLatHeadsPerWarp][kLatVR];
 #pragma unroll
@@ -293,7 +324,20 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
   for (int j0 = k_lo; j0 < k_hi; j0 += 32) {
     const int cnt = min(32, k_hi - j0);
     __syncthreads();
-    for (int i = threadIdx.x; i < cnt * kd; i += blockDim.x) kc[i] = ldf<T>(K + (int64_t)j0 * kd + i);
+    {   // rows j0 … j0+cnt-1 are contiguous in the cache: one flat copy, eight elements a piece where alignment allows
+      const T* src = K + (int64_t)j0 * kd;
+      const int total = cnt * kd;
+      if (p.stage_vec) {
+        for (int i = threadIdx.x * 8; i < total; i += blockDim.x * 8) {
+          float v[8];
+          load8<T>(src + i, v);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) kc[i + u] = v[u];
+        }
+      } else {
+        for (int i = threadIdx.x; i < total; i += blockDim.x) kc[i] = ldf<T>(src + i);
+      }
+    }
     __syncthreads();
 #pragma unroll
     for (int u = 0; u < kLatHeadsPerWarp; ++u) {
@@ -338,34 +382,50 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
     for (int i = 0; i < kLatVR; ++i)
       if (lane + 32 * i < r) dst[2 + lane + 32 * i] = acc[u][i];
   }
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(p.split_tickets + t, 1u);
-  __syncthreads();
-  if (s_ticket != (unsigned)p.nsplit - 1) return;
-  __threadfence();
-  if (threadIdx.x == 0) p.split_tickets[t] = 0;   // ready for the next launch
-  for (int hd = warp; hd < H; hd += 8) {
-    const float* src = p.split_ws + ((int64_t)t * H + hd) * p.nsplit * (2 + r);
-    float M = -INFINITY;
-    for (int sp = 0; sp < p.nsplit; ++sp) M = fmaxf(M, __ldcg(src + (int64_t)sp * (2 + r)));
-    float tot = 0.f, out[kLatVR];
+}
+
+// One CTA per (row, head): the splits' partial softmaxes {max, sum, weighted latents} become the head's weighted latent.
+// The splits' maxima and sums are fetched side by side and turned into one weight per split in shared memory; then
+// every thread sums its columns over the splits (independent loads).
+template <typename T>
+__global__ void __launch_bounds__(256) latent_merge_kernel(const LatentRun p) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float wgt[kLatentMaxSplits];
+  __shared__ float s_tot;
+  const int t = blockIdx.x, hd = blockIdx.y, H = p.a.heads, r = p.l.kv_rank;
+  const float* src = p.split_ws + ((int64_t)t * H + hd) * p.nsplit * (2 + r);
+  const int used = min(p.nsplit, (p.pos[t] + p.keys_per_split) / p.keys_per_split);   // splits that saw a key
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float mx[kLatentMaxSplits / 32], sm_[kLatentMaxSplits / 32], M = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < kLatVR; ++i) out[i] = 0.f;
-    for (int sp = 0; sp < p.nsplit; ++sp) {
-      const float* ps = src + (int64_t)sp * (2 + r);
-      const float ms = __ldcg(ps);
-      if (ms == -INFINITY) continue;
-      const float f = expf(ms - M);
-      tot += f * __ldcg(ps + 1);
-#pragma unroll
-      for (int i = 0; i < kLatVR; ++i)
-        if (lane + 32 * i < r) out[i] = fmaf(f, __ldcg(ps + 2 + lane + 32 * i), out[i]);
+    for (int u = 0; u < kLatentMaxSplits / 32; ++u) {
+      const int sp = lane + 32 * u;
+      mx[u] = sp < used ? src[(int64_t)sp * (2 + r)] : -INFINITY;
+      sm_[u] = sp < used ? src[(int64_t)sp * (2 + r) + 1] : 0.f;
+      M = fmaxf(M, mx[u]);
     }
-    T* orow = static_cast<T*>(p.ol) + ((int64_t)t * H + hd) * r;
+    M = warp_max(M);
+    float tot = 0.f;
 #pragma unroll
-    for (int i = 0; i < kLatVR; ++i)
-      if (lane + 32 * i < r) orow[lane + 32 * i] = cvt<T>(out[i] / tot);
+    for (int u = 0; u < kLatentMaxSplits / 32; ++u) {
+      const int sp = lane + 32 * u;
+      const float w = sp < used ? expf(mx[u] - M) : 0.f;
+      if (sp < kLatentMaxSplits) wgt[sp] = w;
+      tot += w * sm_[u];
+    }
+    tot = warp_sum(tot);
+    if (lane == 0) s_tot = tot;
+  }
+  __syncthreads();
+  const float inv = 1.f / s_tot;
+  T* orow = static_cast<T*>(p.ol) + ((int64_t)t * H + hd) * r;
+  for (int c = threadIdx.x; c < r; c += blockDim.x) {
+    float v = 0.f;
+#pragma unroll 8
+    for (int sp = 0; sp < used; ++sp) v = fmaf(wgt[sp], src[(int64_t)sp * (2 + r) + 2 + c], v);
+    orow[c] = cvt<T>(v * inv);
   }
 }
 
@@ -377,9 +437,51 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
 // while the current one is summed.  Eight columns per CTA.
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-// DR = rows of S per lane (key size <= 32·DR).  Tokens are taken four at a time: while one group is summed, the next
-// group's q, k, v and gate logits are already on their way into registers, so the walk along the sequence waits for
-// memory once per sequence, not once per token.
+// One warp per (sequence, head): the gates of every token — i = cap·tanh(z_i/cap), f = logsigmoid(cap·tanh(z_f/cap)) — the
+// running maximum m_t = max(f + m_(t-1), i) along the sequence (32 tokens' gates are computed side by side, the maximum
+// walks through them), and from it the decay a_t = e^(f + m_(t-1) − m_t) and the input weight b_t = e^(i − m_t).
+// gab[row][head] = {a, b, m}: the column warps of the scan below no longer repeat any of this.
+__global__ void __launch_bounds__(32) mlstm_gates_kernel(const MlstmRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int seg = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x;
+  const int dk = p.a.dim, dv = p.a.vdim, H = p.a.heads;
+  const int r0 = p.seg_row0 != nullptr ? p.seg_row0[seg] : seg;
+  const int cnt = p.seg_count != nullptr ? p.seg_count[seg] : 1;
+  const float* st_m = p.state + (int64_t)p.slot[r0] * p.slot_stride + (int64_t)hd * ((int64_t)dk * (dv + 1) + dv + 1) +
+                      (int64_t)dk * (dv + 1);
+  float m_prev = p.pos[r0] > 0 ? st_m[0] : 0.f;
+  const float cap = p.gate_cap;
+  for (int t0 = 0; t0 < cnt; t0 += 32) {
+    const int t = t0 + lane;
+    float gi = 0.f, gf = 0.f;
+    if (t < cnt) {
+      gi = cap * tanhf(p.gates[(int64_t)(r0 + t) * p.ld_gates + hd] / cap);
+      gf = log_sigmoid(cap * tanhf(p.gates[(int64_t)(r0 + t) * p.ld_gates + H + hd] / cap));
+    }
+    float before = 0.f, after = 0.f;
+    const int n = min(32, cnt - t0);
+    for (int u = 0; u < n; ++u) {
+      const float m_new = fmaxf(__shfl_sync(0xffffffffu, gf, u) + m_prev, __shfl_sync(0xffffffffu, gi, u));
+      if (lane == u) {
+        before = m_prev;
+        after = m_new;
+      }
+      m_prev = m_new;
+    }
+    if (t < cnt) {
+      float* o = p.gab + ((int64_t)(r0 + t) * H + hd) * 3;
+      o[0] = expf(gf + before - after);
+      o[1] = expf(gi - after);
+      o[2] = after;
+    }
+  }
+}
+
+// DR = rows of S per lane (key size <= 32·DR).  One warp per (sequence, head, state column): lane l holds rows l, l + 32, …
+// of its column of S; column vdim is the normaliser n (the column whose "value" is 1).  Tokens are taken four at a time:
+// while one group is summed, the next group's q, k, v and gate factors are already on their way into registers, so the
+// walk along the sequence waits for memory once per sequence, not once per token.  Eight columns per CTA.
 template <typename T, int DR>
 __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
   pdl_trigger();
@@ -400,11 +502,10 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
     const int d = lane + 32 * i;
     S[i] = (pos0 > 0 && d < dk) ? st[(int64_t)d * (dv + 1) + j] : 0.f;
   }
-  if (pos0 > 0) m = st_m[j];
-  const float qs = rsqrtf((float)dk), cap = p.gate_cap;
+  const float qs = rsqrtf((float)dk);
   const T* P = static_cast<const T*>(p.proj);
   struct Tok {
-    float q[DR], k[DR], v, zi, zf;
+    float q[DR], k[DR], v, a, b, m;
   };
   Tok cur[PF], nxt[PF];
   auto fetch = [&](Tok& o, int t) {
@@ -418,8 +519,10 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
       o.k[i] = (ok && d < dk) ? ldf<T>(pr + p.off_k + hd * dk + d) : 0.f;
     }
     o.v = (ok && j < dv) ? ldf<T>(pr + p.off_v + hd * dv + j) : 1.f;
-    o.zi = ok ? p.gates[(int64_t)row * p.ld_gates + hd] : 0.f;
-    o.zf = ok ? p.gates[(int64_t)row * p.ld_gates + H + hd] : 0.f;
+    const float* g = p.gab + ((int64_t)row * H + hd) * 3;
+    o.a = g[0];
+    o.b = g[1];
+    o.m = g[2];
   };
 #pragma unroll
   for (int u = 0; u < PF; ++u) fetch(nxt[u], u);
@@ -430,17 +533,10 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
 #pragma unroll
       for (int u = 0; u < PF; ++u) fetch(nxt[u], g0 + PF + u);
     }
-    float gi[PF], gf[PF];
-#pragma unroll
-    for (int u = 0; u < PF; ++u) {
-      gi[u] = cap * tanhf(cur[u].zi / cap);
-      gf[u] = log_sigmoid(cap * tanhf(cur[u].zf / cap));
-    }
 #pragma unroll
     for (int u = 0; u < PF; ++u) {
       if (g0 + u >= cnt) break;
-      const float m_new = fmaxf(gf[u] + m, gi[u]);
-      const float a = expf(gf[u] + m - m_new), b = expf(gi[u] - m_new) * cur[u].v;
+      const float a = cur[u].a, b = cur[u].b * cur[u].v;
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < DR; ++i) {
@@ -448,7 +544,7 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
         dot = fmaf(S[i], cur[u].q[i] * qs, dot);
       }
       dot = warp_sum(dot);
-      m = m_new;
+      m = cur[u].m;
       if (lane == 0) {
         float* orow = p.o + ((int64_t)(r0 + g0 + u) * H + hd) * (dv + 2);
         orow[j] = dot;
@@ -586,7 +682,10 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const MoeRun p) {
   if (p.shared != nullptr) gate = 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
   for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
     float v = 0.f;
-    for (int k = 0; k < top; ++k) v += p.outp[(int64_t)p.pair_slot[(int64_t)t * top + k] * p.width + i];
+    for (int k = 0; k < top; ++k) {
+      const int64_t o = (int64_t)p.pair_slot[(int64_t)t * top + k] * p.width + i;
+      v += p.tc ? __bfloat162float(p.outp_bf[o]) : p.outp[o];
+    }
     if (p.shared != nullptr) {
       const int64_t o = (int64_t)t * p.width + i;
       v += gate * (p.shared_f32 ? static_cast<const float*>(p.shared)[o] : ldf<T>(static_cast<const T*>(p.shared) + o));
@@ -672,6 +771,31 @@ int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st) {
   return B200_OK;
 }
 
+int launch_skinny_f32(float* C, const void* A, const void* W, const float* bias, int rows, int n, int K, int dtype,
+                      cudaStream_t st) {
+  SmallGemv g;
+  g.a = W; g.lda = K; g.sa = (int64_t)kSmallRows * K;
+  g.w = A; g.sw = 0;
+  g.c = C; g.ldc = 1; g.sc = kSmallRows; g.nc = n; g.c_f32 = true;
+  g.M = kSmallRows; g.m_total = n; g.N = rows; g.K = K; g.items = (n + kSmallRows - 1) / kSmallRows;
+  g.bias_m = bias;
+  return launch_small_gemv(g, dtype, st);
+}
+
+int launch_latent_pack(const LatentPack& p, cudaStream_t st) {
+  B200_CHECK_ARG(p.kp && p.cache_rows && p.proj && p.qa && p.kbuf && p.qbuf && p.ctx > 0 && p.count > 0, "latent pack: null argument");
+  B200_CUDA(launch_pdl(latent_pack_kernel, dim3(p.ctx + p.count), dim3(128), 0, st, false, p));
+  return B200_OK;
+}
+
+int launch_latent_prep(const LatentRun& p, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(p.proj && p.cache && p.slot && p.pos && p.qa && p.n_tok > 0, "latent prep: null argument");
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(latent_prep_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  return B200_OK;
+}
+
 int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
   const int r = p.l.kv_rank, dr = p.l.rot_dim, H = p.a.heads, dn = p.a.dim, kd = r + dr;
@@ -711,8 +835,17 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
       attr_done = true;
     }
     const dim3 grid(p.n_tok, p.nsplit);
-    if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_split_kernel<float>, grid, dim3(256), split_smem, st, stack_pdl(), p));
-    else B200_CUDA(launch_pdl(latent_attn_split_kernel<__nv_bfloat16>, grid, dim3(256), split_smem, st, stack_pdl(), p));
+    LatentRun q = p;
+    const size_t al = dtype == B200_F32 ? 32 : 16;
+    q.stage_vec = ((size_t)kd * esz) % al == 0 && (reinterpret_cast<uintptr_t>(p.cache) % al) == 0 &&
+                  ((size_t)p.slot_stride * esz) % al == 0 && (32 * kd) % 8 == 0;
+    if (dtype == B200_F32) {
+      B200_CUDA(launch_pdl(latent_attn_split_kernel<float>, grid, dim3(256), split_smem, st, stack_pdl(), q));
+      B200_CUDA(launch_pdl(latent_merge_kernel<float>, dim3(p.n_tok, H), dim3(256), 0, st, stack_pdl(), q));
+    } else {
+      B200_CUDA(launch_pdl(latent_attn_split_kernel<__nv_bfloat16>, grid, dim3(256), split_smem, st, stack_pdl(), q));
+      B200_CUDA(launch_pdl(latent_merge_kernel<__nv_bfloat16>, dim3(p.n_tok, H), dim3(256), 0, st, stack_pdl(), q));
+    }
   } else {
     const size_t smem = (size_t)(kd + 4 * (2 + r)) * 4;
     if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
@@ -740,6 +873,8 @@ int run_mlstm(const MlstmRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(p.proj && p.gates && p.state && p.slot && p.pos && p.o && p.n_seg > 0 && p.n_tok > 0, "mlstm: null argument");
   B200_CHECK_ARG(p.a.heads > 0 && p.a.dim > 0 && p.a.vdim > 0 && p.gate_cap > 0.f, "mlstm: bad sizes");
   B200_CHECK_ARG(p.a.dim <= kMlstmMaxDim, "mlstm: key size above %d not built", kMlstmMaxDim);
+  B200_CHECK_ARG(p.gab != nullptr, "mlstm: null gate workspace");
+  B200_CUDA(launch_pdl(mlstm_gates_kernel, dim3(p.n_seg, p.a.heads), dim3(32), 0, st, stack_pdl(), p));
   const dim3 grid(p.n_seg, p.a.heads, (p.a.vdim + 1 + 7) / 8);
 #define B200_SCAN(DR)                                                                                              \
   do {                                                                                                             \
@@ -791,15 +926,62 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
     d.c = p.outp; d.sc = p.width; d.c_f32 = true; d.M = 1; d.N = p.width; d.K = m.expert_ff; d.items = P;
     if ((rc = launch_small_gemv(d, dtype, st)) != B200_OK) return rc;
   } else {
-  StackGemm rz;   // router logits in fp32
-  rz.a = p.h; rz.lda = p.width; rz.k1 = p.width;
-  rz.w = m.router; rz.M = p.n_tok; rz.N = E; rz.K = p.width;
-  rz.epi = SEPI_STORE_F32; rz.c = p.z; rz.ldc = E;
-  if ((rc = launch_stack_gemm(rz, dtype, st)) != B200_OK) return rc;
+  // router logits in fp32
+  if ((rc = launch_skinny_f32(p.z, p.h, m.router, nullptr, p.n_tok, E, p.width, dtype, st)) != B200_OK) return rc;
   B200_CUDA(launch_pdl(moe_route_kernel, dim3((p.n_tok + 3) / 4), dim3(128), 0, st, stack_pdl(), p));
   B200_CUDA(launch_pdl(moe_plan_kernel, dim3(1), dim3(256), (size_t)E * 4, st, stack_pdl(), p));
   if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+  if (p.tc) {
+    B200_CHECK_ARG(dtype == B200_BF16 && p.outp_bf != nullptr, "moe: the tensor-core path is bf16");
+    std::vector<int32_t> ends(E);
+    B200_CUDA(cudaMemcpyAsync(ends.data(), p.plan + E, (size_t)E * 4, cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaStreamSynchronize(st));
+    const __nv_bfloat16* A = (const __nv_bfloat16*)p.a_perm;
+    __nv_bfloat16 *GU = (__nv_bfloat16*)p.gu, *ACT = (__nv_bfloat16*)p.act;
+    const int64_t f2 = 2ll * m.expert_ff;
+    // one expert's rows rarely fill the GPU: the experts' products go round four side streams that fork from and join
+    // back into the step's stream
+    constexpr int kSide = 4;
+    static cudaStream_t side[kSide];
+    static cudaEvent_t fork_ev, join_ev[kSide];
+    static bool side_ok = false;
+    if (!side_ok) {
+      for (int i = 0; i < kSide; ++i) {
+        B200_CUDA(cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking));
+        B200_CUDA(cudaEventCreateWithFlags(&join_ev[i], cudaEventDisableTiming));
+      }
+      B200_CUDA(cudaEventCreateWithFlags(&fork_ev, cudaEventDisableTiming));
+      side_ok = true;
+    }
+    auto fork = [&]() -> int {
+      B200_CUDA(cudaEventRecord(fork_ev, st));
+      for (int i = 0; i < kSide; ++i) B200_CUDA(cudaStreamWaitEvent(side[i], fork_ev, 0));
+      return B200_OK;
+    };
+    auto join = [&]() -> int {
+      for (int i = 0; i < kSide; ++i) {
+        B200_CUDA(cudaEventRecord(join_ev[i], side[i]));
+        B200_CUDA(cudaStreamWaitEvent(st, join_ev[i], 0));
+      }
+      return B200_OK;
+    };
+    if ((rc = fork()) != B200_OK) return rc;
+    for (int e = 0, row = 0, n = 0; e < E; row = ends[e], ++e)
+      if (ends[e] > row && (rc = launch_gemm_bf16(GU + (int64_t)row * f2, A + (int64_t)row * p.width,
+                                                  (const __nv_bfloat16*)m.w_exp_in + (int64_t)e * f2 * p.width, ends[e] - row, f2,
+                                                  p.width, side[n++ % kSide])) != B200_OK)
+        return rc;
+    if ((rc = join()) != B200_OK) return rc;
+    if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, f2, P, m.expert_ff, m.limit, dtype, st)) != B200_OK) return rc;
+    if ((rc = fork()) != B200_OK) return rc;
+    for (int e = 0, row = 0, n = 0; e < E; row = ends[e], ++e)
+      if (ends[e] > row && (rc = launch_gemm_bf16(p.outp_bf + (int64_t)row * p.width, ACT + (int64_t)row * m.expert_ff,
+                                                  (const __nv_bfloat16*)m.w_exp_out + (int64_t)e * p.width * m.expert_ff,
+                                                  ends[e] - row, p.width, m.expert_ff, side[n++ % kSide])) != B200_OK)
+        return rc;
+    if ((rc = join()) != B200_OK) return rc;
+  } else {
   StackGemm g;
   g.a = p.a_perm; g.lda = p.width; g.k1 = p.width;
   g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width;
@@ -816,6 +998,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   d.epi = SEPI_STORE_F32; d.c = p.outp; d.ldc = p.width;
   d.tile_group = g.tile_group; d.tile_row0 = g.tile_row0; d.group_end = g.group_end; d.n_tiles = n_tiles;
   if ((rc = launch_stack_gemm(d, dtype, st)) != B200_OK) return rc;
+  }
   }
   if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));

@@ -34,8 +34,16 @@ struct SmallGemv {
   int64_t ldc = 0, sc = 0;
   bool c_f32 = false;
   int M = 1, N = 0, K = 0, items = 1;
+  int64_t nc = 1;                // stride of the output row index n inside c
+  int m_total = 0;               // > 0: item z has min(M, m_total − z·M) rows (the last item may be short)
+  const float* bias_m = nullptr; // [m_total]: bias of row z·M + m
 };
 int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st);
+// C[rows, n] (fp32) = A[rows, K]·W[n, K]ᵀ + bias[n] for a FEW output columns n and any number of rows (router and gate
+// logits of a prompt): the small product with the roles swapped — W's rows, eight at a time, are the "activations", A's
+// rows the matrix.
+int launch_skinny_f32(float* C, const void* A, const void* W, const float* bias_or_null, int rows, int n, int K, int dtype,
+                      cudaStream_t st);
 
 // ---- latent attention: everything between the in-projection and the out-projection
 constexpr int kLatentMaxRank = 512;
@@ -57,14 +65,34 @@ struct LatentRun {
   int64_t ld_out = 0;
   // decode-shaped steps (up to kSmallRows rows, long key lists): one CTA per (row, split of the key list) serves ALL heads
   // from key rows staged once in shared memory; the partial softmaxes [row][head][split][2 + kv_rank] in split_ws are
-  // merged by the CTA that finishes a row last (split_tickets [row], zero-initialised, self-resetting)
+  // joined by a second small launch
   float* split_ws = nullptr;
-  unsigned int* split_tickets = nullptr;
   int nsplit = 0, keys_per_split = 0;
+  bool stage_vec = false;        // set by the launcher: the staged rows can be copied in 16-byte pieces
 };
-constexpr int kLatentMaxSplits = 32;
-constexpr int kLatentSplitKeys = 128;
+constexpr int kLatentMaxSplits = 128;
+constexpr int kLatentSplitKeys = 32;
 int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st);
+// the first step alone: cache rows and rotated query parts of the new tokens
+int launch_latent_prep(const LatentRun& p, int dtype, cudaStream_t st);
+// Prompt-shaped steps of bf16 engines whose heads suit the tensor-core attention kernel (dim + rot_dim == vdim): the keys
+// and values of ONE sequence are expanded from its cache rows and laid out per head.
+//   kbuf[j, h, :] = [kp[j, h·dim …] | rotated key part of cache row j]        j < ctx      (kp = latents · ukᵀ)
+//   qbuf[t, h, :] = [q_plain of row row0 + t, head h | its rotated part from qa]            t < count
+struct LatentPack {
+  b200_attn_desc a{};
+  b200_latent_desc l{};
+  const __nv_bfloat16* kp = nullptr;       // [ctx, heads·dim]
+  const __nv_bfloat16* cache_rows = nullptr;   // the sequence's cache rows [ctx][kv_rank + rot_dim]
+  const __nv_bfloat16* proj = nullptr;     // the sequence's first row of the merged projection
+  int64_t ld_proj = 0;
+  int off_q = 0;
+  const __nv_bfloat16* qa = nullptr;       // the sequence's first row of qa
+  __nv_bfloat16* kbuf = nullptr;           // [ctx, heads·(dim + rot_dim)]
+  __nv_bfloat16* qbuf = nullptr;           // [count, heads·(dim + rot_dim)]
+  int ctx = 0, count = 0;
+};
+int launch_latent_pack(const LatentPack& p, cudaStream_t st);
 
 // ---- mLSTM: recurrence + head norm + output gate
 constexpr int kMlstmMaxDim = 512;
@@ -83,6 +111,7 @@ struct MlstmRun {
   const int32_t* slot = nullptr;       // per row
   const int32_t* pos = nullptr;        // per row
   int n_seg = 0, n_tok = 0;
+  float* gab = nullptr;          // [n_tok, heads, 3] fp32 workspace: decay, input weight, running maximum of every token
   float* o = nullptr;            // [n_tok, heads·(vdim + 2)] fp32: numerators | n·q | m
   const float* head_norm = nullptr;
   void* mid = nullptr;           // [n_tok, ld_mid] T: normed, gated head outputs
@@ -114,6 +143,10 @@ struct MoeRun {
   // steps of up to kSmallRows tokens: no sorting — every (token, choice) pair is an item of a small product with its
   // expert's matrices
   bool small = false;
+  // bf16 steps of many rows: the group sizes are read back to the host (one small copy and a wait per feed-forward) and
+  // every expert's rows go through the tcgen05 GEMM; the down-projections leave bf16 rows in outp_bf
+  bool tc = false;
+  __nv_bfloat16* outp_bf = nullptr;   // [P, width]
 };
 __host__ __device__ inline int moe_tiles(int pairs, int experts) { return (pairs + 63) / 64 + experts; }
 inline int64_t moe_plan_ints(int pairs, int experts) { return 2 * (int64_t)experts + 2 * moe_tiles(pairs, experts); }

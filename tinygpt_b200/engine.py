@@ -195,7 +195,8 @@ class DecodeEngine:
             tab = self._rot_tables.get(a.rot)
             if tab is None and a.rot.dims > 0:
                 tab = self._rot_tables[a.rot] = a.rot.table(spec.max_ctx).contiguous().to(self.device)
-            lat = LatentDesc(a.kv_rank, a.rot_dim, a.rot.dims, ptr(p + "c_norm", f32), ptr(p + "uk_t", mdt), ptr(p + "uv", mdt),
+            lat = LatentDesc(a.kv_rank, a.rot_dim, a.rot.dims, ptr(p + "c_norm", f32), ptr(p + "uk_t", mdt), ptr(p + "uk", mdt),
+                             ptr(p + "uv", mdt),
                              tab.data_ptr() if tab is not None else None)
             mixer = 1
         else:

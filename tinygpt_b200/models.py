@@ -573,8 +573,8 @@ def synth_silatar_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> 
 def pack_silatar_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
                          dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
     """Checkpoint tensors (Silatar names) → the engine's layout on `device`.  Per layer: w_in = the mixer's in-projections
-    merged by rows (StackSpec.mix_layout), b_in fp32 (the mLSTM gates' biases), w_out = mix.o; latent attention: uk
-    transposed per head [heads, kv_rank, dim], uv as stored; dense feed-forward: up / down; experts: gate|up of all experts
+    merged by rows (StackSpec.mix_layout), b_in fp32 (the mLSTM gates' biases), w_out = mix.o; latent attention: uk both
+    as stored and transposed per head [heads, kv_rank, dim], uv as stored; dense feed-forward: up / down; experts: gate|up of all experts
     as one [experts, 2·ff, width] block and down as [experts, width, ff]; shared expert: [gate | up | shared-gate row]
     (padded to 8 rows) and down.  Vectors in fp32, matrices in `dtype`."""
     W = spec.width
@@ -604,6 +604,7 @@ def pack_silatar_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device
             put(lay.off_k, "mix.dkv")
             out[p + "c_norm"] = vec(named[p + "mix.dkv.norm"])
             out[p + "uk_t"] = mat(named[p + "mix.uk"].view(a.heads, a.dim, a.kv_rank).transpose(1, 2))
+            out[p + "uk"] = mat(named[p + "mix.uk"])
             out[p + "uv"] = mat(named[p + "mix.uv"])
         else:
             a = L.mlstm

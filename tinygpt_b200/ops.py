@@ -334,7 +334,8 @@ def stack_latent_attention(proj: torch.Tensor, off_down: int, cache: torch.Tenso
     import ctypes as C
     from ._lib import LatentDesc
     a = _attn_desc(heads, 1, dim, vdim, scale, 0, 0, 0)
-    l = LatentDesc(int(kv_rank), int(rot_dim), int(rot_dims), c_norm.data_ptr(), uk_t.data_ptr(), uv.data_ptr(), _ptr(rot_table))
+    l = LatentDesc(int(kv_rank), int(rot_dim), int(rot_dims), c_norm.data_ptr(), uk_t.data_ptr(), None, uv.data_ptr(),
+                   _ptr(rot_table))
     out = torch.empty(proj.shape[0], heads * vdim, dtype=proj.dtype, device=proj.device)
     check(lib().b200_stack_latent_attention(out.data_ptr(), out.stride(0), proj.data_ptr(), proj.stride(0), int(off_down),
                                             cache.data_ptr(), cache.stride(0), slot.data_ptr(), pos.data_ptr(), proj.shape[0],

@@ -123,7 +123,9 @@ def device_silatar_weights(spec: models.StackSpec, device, seed: int = 0) -> Dic
         w[p + "w_in"], w[p + "b_in"], w[p + "w_out"] = mat(lay.n_in, W), vec(lay.n_in, 0.0), mat(W, lay.k_out)
         if L.mixer == "latent_attention":
             a = L.latent
-            w[p + "c_norm"], w[p + "uk_t"], w[p + "uv"] = vec(a.kv_rank), mat(a.heads, a.kv_rank, a.dim), mat(a.heads * a.vdim, a.kv_rank)
+            w[p + "c_norm"], w[p + "uv"] = vec(a.kv_rank), mat(a.heads * a.vdim, a.kv_rank)
+            w[p + "uk"] = mat(a.heads * a.dim, a.kv_rank)
+            w[p + "uk_t"] = w[p + "uk"].view(a.heads, a.dim, a.kv_rank).transpose(1, 2).contiguous()
         else:
             w[p + "head_norm"] = vec(L.mlstm.heads * L.mlstm.vdim)
             w[p + "b_in"][lay.off_gate + L.mlstm.heads:lay.off_gate + 2 * L.mlstm.heads] += 3.0   # a memory that keeps
