@@ -116,6 +116,7 @@ struct StackEngine {
   __nv_bfloat16 *lat_c = nullptr, *lat_kp = nullptr, *lat_k = nullptr, *lat_v = nullptr, *lat_q = nullptr;   // one sequence's expanded keys / values
   int qa_max = 0, ol_max = 0, rec_o_max = 0, moe_e_max = 0, moe_top_max = 0, moe_ff_max = 0, lin_max = 0;
   bool any_rec = false, any_moe = false;
+  bool h_ready = false;            // the previous sublayer's fused post-norm already left this run's normed input in h
   struct SPlans {
     GemvPlan in{}, out{}, ff_in{}, ff_out{};
     bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false;
@@ -519,17 +520,26 @@ static int stack_lin(StackEngine* s, const void* A, const void* Wt, const float*
 }
 
 // x += norm(A·Wᵀ)·w  — a sublayer's out-projection, its post-norm and the residual sum (fp32)
-static int stack_lin_norm_add(StackEngine* s, const void* A, const void* Wt, int M, int K, const GemvPlan* plan,
-                              const float* norm_w, float* x, cudaStream_t st) {
+// x += norm(y)·w, and — when the next sublayer's pre-norm weight is given — h = norm(x)·next_w in the same pass
+static int stack_norm_add_next(StackEngine* s, float* x, const void* y, bool y_bf16, const float* norm_w, const float* next_w,
+                               int M, cudaStream_t st) {
   const b200_stack_desc& d = s->d;
-  const int W = d.width;
+  if (next_w != nullptr)
+    return launch_stack_norm_add_norm(x, y, y_bf16, norm_w, s->h, next_w, M, d.width, d.norm_eps, d.norm_offset, d.residual_mult,
+                                      d.norm_kind, s->dtype, st);
+  return launch_stack_norm_add(x, y, y_bf16, norm_w, M, d.width, d.norm_eps, d.residual_mult, d.norm_kind, st);
+}
+
+static int stack_lin_norm_add(StackEngine* s, const void* A, const void* Wt, int M, int K, const GemvPlan* plan,
+                              const float* norm_w, float* x, const float* next_w, cudaStream_t st) {
+  const int W = s->d.width;
   int rc;
   if (s->fast && !(M <= kMaxBatch && plan != nullptr) && M >= kGemmRows && gemm_shape_ok(W, K)) {
     if ((rc = launch_gemm_bf16(s->lin_tmp, A, Wt, M, W, K, st)) != B200_OK) return rc;
-    return launch_stack_norm_add(x, s->lin_tmp, true, norm_w, M, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+    return stack_norm_add_next(s, x, s->lin_tmp, true, norm_w, next_w, M, st);
   }
   if ((rc = stack_lin(s, A, Wt, nullptr, M, W, K, plan, nullptr, s->y, st)) != B200_OK) return rc;
-  return launch_stack_norm_add(x, s->y, false, norm_w, M, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+  return stack_norm_add_next(s, x, s->y, false, norm_w, next_w, M, st);
 }
 
 static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaStream_t st) {
@@ -540,9 +550,14 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   const int W = d.width, dt = s->dtype;
   const size_t esz = s->esz;
   int rc;
+  // every sublayer's post-norm hands the next sublayer its normed input in the same pass; only the first run norms alone
+  const bool has_ff = !(L.ff_kind == B200_FF_DENSE && L.ff <= 0);
+  const float* next_run_w = r + 1 < d.n_runs ? s->layers[s->run_layer[r + 1]].norm : nullptr;
   // ---- mixer
-  if ((rc = launch_stack_norm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
+  if (!s->h_ready &&
+      (rc = launch_stack_norm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
     return rc;
+  s->h_ready = false;
   const bool rec = L.mixer == B200_MIX_MLSTM;
   const bool gemv_in = s->fast && n_tok <= kMaxBatch && pl.ok_in;
   // an mLSTM's gate logits stay fp32: the GEMV hands out its unrounded sums, the other paths run the gate rows again
@@ -634,17 +649,21 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     m.gab = s->rec_ab; m.o = s->rec_o; m.head_norm = L.rec.head_norm; m.mid = s->mid; m.ld_mid = L.k_out;
     if ((rc = run_mlstm(m, dt, st)) != B200_OK) return rc;
   }
-  if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x, st)) != B200_OK)
+  if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x,
+                               has_ff ? L.ff_norm : next_run_w, st)) != B200_OK)
     return rc;
   // ---- feed-forward
-  if (L.ff_kind == B200_FF_DENSE && L.ff <= 0) return B200_OK;
-  if ((rc = launch_stack_norm(s->h, x, L.ff_norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
-    return rc;
+  if (!has_ff) {
+    s->h_ready = next_run_w != nullptr;
+    return B200_OK;
+  }
+  s->h_ready = next_run_w != nullptr;
   if (L.ff_kind == B200_FF_DENSE) {
     if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, L.ff, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
       return rc;
     if ((rc = launch_stack_act_mul(s->mid, L.ff, s->proj, nullptr, L.ff, n_tok, L.ff, L.ff_act, dt, st)) != B200_OK) return rc;
-    return stack_lin_norm_add(s, s->mid, L.w_ff_out, n_tok, L.ff, pl.ok_ff_out ? &pl.ff_out : nullptr, L.ff_post_norm, x, st);
+    return stack_lin_norm_add(s, s->mid, L.w_ff_out, n_tok, L.ff, pl.ok_ff_out ? &pl.ff_out : nullptr, L.ff_post_norm, x,
+                              next_run_w, st);
   }
   MoeRun m = s->moe_ws;
   m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
@@ -666,7 +685,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     m.sg = (const uint8_t*)s->proj + (size_t)2 * fs * esz; m.ld_sg = n_sh;
   }
   if ((rc = run_moe(m, dt, st)) != B200_OK) return rc;
-  return launch_stack_norm_add(x, s->y, false, L.ff_post_norm, n_tok, W, d.norm_eps, d.residual_mult, d.norm_kind, st);
+  return stack_norm_add_next(s, x, s->y, false, L.ff_post_norm, next_run_w, n_tok, st);
 }
 
 // One pass: n_tok rows {m_tok, m_slot, m_pos} through every run, then the head for the n_rows rows listed in m_want.
@@ -679,6 +698,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bo
   if ((rc = launch_stack_embed(s->x, s->x0, d.embed, s->m_tok, n_tok, d.vocab, W, d.embed_scale, dt, st)) != B200_OK)
     return rc;
   float *cur = s->x, *other = s->x_alt;
+  s->h_ready = false;
   if (s->any_rec && !s->segs.empty()) {   // the recurrences walk every sequence's rows in order
     std::vector<int32_t> sr(2 * s->segs.size());
     for (size_t i = 0; i < s->segs.size(); ++i) {

@@ -62,6 +62,63 @@ __global__ void __launch_bounds__(256) stack_layernorm_kernel(YT* __restrict__ y
   }
 }
 
+// A sublayer's post-norm, the residual sum and the next sublayer's pre-norm in one pass over the row:
+//   x ← x + mult·LN(y)·w_post (fp32, stored),   h ← T(LN(x)·(offset + w_next))
+// One CTA per row; the new x stays in registers between the two norms (dim <= 256·kLn2Regs).
+constexpr int kLn2Regs = 32;
+template <typename YT, typename HT>
+__global__ void __launch_bounds__(256) stack_layernorm2_kernel(float* __restrict__ x, const YT* __restrict__ y,
+                                                               const float* __restrict__ w_post, HT* __restrict__ h,
+                                                               const float* __restrict__ w_next, int dim, float eps,
+                                                               float offset, float mult) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[8];
+  const int64_t base = (int64_t)blockIdx.x * dim;
+  float v[kLn2Regs];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < kLn2Regs; ++u) {
+    const int i = threadIdx.x + 256 * u;
+    v[u] = i < dim ? ldf<YT>(y + base + i) : 0.f;
+    s += v[u];
+  }
+  float mean = block_sum(s, red) / (float)dim, q = 0.f;
+#pragma unroll
+  for (int u = 0; u < kLn2Regs; ++u) {
+    const int i = threadIdx.x + 256 * u;
+    const float d = i < dim ? v[u] - mean : 0.f;
+    q += d * d;
+  }
+  float inv = rsqrtf(block_sum(q, red) / (float)dim + eps);
+  s = 0.f;
+#pragma unroll
+  for (int u = 0; u < kLn2Regs; ++u) {
+    const int i = threadIdx.x + 256 * u;
+    if (i < dim) {
+      v[u] = x[base + i] + mult * (v[u] - mean) * inv * w_post[i];
+      x[base + i] = v[u];
+      s += v[u];
+    } else {
+      v[u] = 0.f;
+    }
+  }
+  mean = block_sum(s, red) / (float)dim;
+  q = 0.f;
+#pragma unroll
+  for (int u = 0; u < kLn2Regs; ++u) {
+    const int i = threadIdx.x + 256 * u;
+    const float d = i < dim ? v[u] - mean : 0.f;
+    q += d * d;
+  }
+  inv = rsqrtf(block_sum(q, red) / (float)dim + eps);
+#pragma unroll
+  for (int u = 0; u < kLn2Regs; ++u) {
+    const int i = threadIdx.x + 256 * u;
+    if (i < dim) h[base + i] = cvt<HT>((v[u] - mean) * inv * (offset + w_next[i]));
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------- elementwise
 template <typename T>
 __global__ void __launch_bounds__(256) stack_glu_clamp_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ gu,
@@ -308,10 +365,19 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
   float* q = sm;                          // [H][kd], scaled
   float* kc = sm + (size_t)H * kd;        // [32][kd] staged key rows
   const T* qrow = static_cast<const T*>(p.qa) + (int64_t)t * H * kd;
-  for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
   const int n_keys = p.pos[t] + 1;
   const int k_lo = split * p.keys_per_split, k_hi = min(n_keys, k_lo + p.keys_per_split);
   if (k_lo >= n_keys) return;   // the merge reads the splits that saw a key, and only those
+  if (p.stage_vec) {
+    for (int i = threadIdx.x * 8; i < H * kd; i += blockDim.x * 8) {
+      float v[8];
+      load8<T>(qrow + i, v);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) q[i + u] = v[u] * p.a.scale;
+    }
+  } else {
+    for (int i = threadIdx.x; i < H * kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
+  }
   const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
   float m[kLatHeadsPerWarp], sum[kLatHeadsPerWarp], acc[kLatHeadsPerWarp][kLatVR];
 #pragma unroll
@@ -479,18 +545,25 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(const MlstmRun p) {
 }
 
 // DR = rows of S per lane (key size <= 32·DR).  One warp per (sequence, head, state column): lane l holds rows l, l + 32, …
-// of its column of S; column vdim is the normaliser n (the column whose "value" is 1).  Tokens are taken four at a time:
-// while one group is summed, the next group's q, k, v and gate factors are already on their way into registers, so the
-// walk along the sequence waits for memory once per sequence, not once per token.  Eight columns per CTA.
+// of its column of S; column vdim is the normaliser n (the column whose "value" is 1); eight columns per CTA.  The CTA
+// walks its sequence CH tokens at a time: the chunk's q (scaled), k, the eight columns' v and the gate factors sit in
+// shared memory as fp32, converted once for all eight warps, while the next chunk's values are already on their way
+// into registers — the walk waits for memory once per sequence, and a token costs a warp a handful of shared-memory
+// reads, 2·DR multiply-adds and one warp sum.
 template <typename T, int DR>
 __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
   pdl_trigger();
   pdl_wait();
-  constexpr int PF = DR >= 16 ? 2 : 4;
-  const int seg = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int CH = DR >= 16 ? 8 : 16;          // tokens per chunk
+  constexpr int DK = 32 * DR;                    // padded key size
+  constexpr int NQK = CH * 2 * DK / 256;         // q / k elements a thread stages per chunk
+  __shared__ float s_qk[CH][2][DK];
+  __shared__ float s_ab[CH][3];
+  __shared__ float s_v[CH][8];
+  const int seg = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int dk = p.a.dim, dv = p.a.vdim, H = p.a.heads;
-  const int j = blockIdx.z * 8 + warp;
-  if (j > dv) return;
+  const int j0 = blockIdx.z * 8, j = j0 + warp;
+  const bool live = j <= dv;                     // warps past the last column only help with the staging
   const int r0 = p.seg_row0 != nullptr ? p.seg_row0[seg] : seg;
   const int cnt = p.seg_count != nullptr ? p.seg_count[seg] : 1;
   const int pos0 = p.pos[r0];
@@ -500,58 +573,58 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
 #pragma unroll
   for (int i = 0; i < DR; ++i) {
     const int d = lane + 32 * i;
-    S[i] = (pos0 > 0 && d < dk) ? st[(int64_t)d * (dv + 1) + j] : 0.f;
+    S[i] = (live && pos0 > 0 && d < dk) ? st[(int64_t)d * (dv + 1) + j] : 0.f;
   }
   const float qs = rsqrtf((float)dk);
   const T* P = static_cast<const T*>(p.proj);
-  struct Tok {
-    float q[DR], k[DR], v, a, b, m;
-  };
-  Tok cur[PF], nxt[PF];
-  auto fetch = [&](Tok& o, int t) {
-    const bool ok = t < cnt;
-    const int row = r0 + (ok ? t : 0);
-    const T* pr = P + (int64_t)row * p.ld_proj;
+  float r_qk[NQK], r_x = 0.f;   // staged values of the next chunk; r_x: a gate factor (threads 0 … 3·CH) or a v (next 8·CH)
+  auto fetch = [&](int c0) {
 #pragma unroll
-    for (int i = 0; i < DR; ++i) {
-      const int d = lane + 32 * i;
-      o.q[i] = (ok && d < dk) ? ldf<T>(pr + p.off_q + hd * dk + d) : 0.f;
-      o.k[i] = (ok && d < dk) ? ldf<T>(pr + p.off_k + hd * dk + d) : 0.f;
+    for (int i = 0; i < NQK; ++i) {
+      const int e = tid + 256 * i, t = e / (2 * DK), w = (e / DK) & 1, d = e % DK;
+      r_qk[i] = (c0 + t < cnt && d < dk) ? ldf<T>(P + (int64_t)(r0 + c0 + t) * p.ld_proj + (w ? p.off_k : p.off_q) + hd * dk + d)
+                                         : 0.f;
     }
-    o.v = (ok && j < dv) ? ldf<T>(pr + p.off_v + hd * dv + j) : 1.f;
-    const float* g = p.gab + ((int64_t)row * H + hd) * 3;
-    o.a = g[0];
-    o.b = g[1];
-    o.m = g[2];
-  };
-#pragma unroll
-  for (int u = 0; u < PF; ++u) fetch(nxt[u], u);
-  for (int g0 = 0; g0 < cnt; g0 += PF) {
-#pragma unroll
-    for (int u = 0; u < PF; ++u) cur[u] = nxt[u];
-    if (g0 + PF < cnt) {
-#pragma unroll
-      for (int u = 0; u < PF; ++u) fetch(nxt[u], g0 + PF + u);
+    if (tid < 3 * CH) {
+      const int t = tid / 3;
+      r_x = c0 + t < cnt ? p.gab[((int64_t)(r0 + c0 + t) * H + hd) * 3 + tid % 3] : 0.f;
+    } else if (tid < 11 * CH) {
+      const int t = (tid - 3 * CH) / 8, c = j0 + (tid - 3 * CH) % 8;
+      r_x = (c0 + t < cnt && c < dv) ? ldf<T>(P + (int64_t)(r0 + c0 + t) * p.ld_proj + p.off_v + hd * dv + c) : 1.f;
     }
+  };
+  fetch(0);
+  for (int c0 = 0; c0 < cnt; c0 += CH) {
+    __syncthreads();   // the previous chunk has been read
 #pragma unroll
-    for (int u = 0; u < PF; ++u) {
-      if (g0 + u >= cnt) break;
-      const float a = cur[u].a, b = cur[u].b * cur[u].v;
+    for (int i = 0; i < NQK; ++i) {
+      const int e = tid + 256 * i, w = (e / DK) & 1;
+      (&s_qk[0][0][0])[e] = w ? r_qk[i] : r_qk[i] * qs;
+    }
+    if (tid < 3 * CH) (&s_ab[0][0])[tid] = r_x;
+    else if (tid < 11 * CH) (&s_v[0][0])[tid - 3 * CH] = r_x;
+    __syncthreads();
+    if (c0 + CH < cnt) fetch(c0 + CH);
+    if (!live) continue;
+    const int n = min(CH, cnt - c0);
+    for (int t = 0; t < n; ++t) {
+      const float a = s_ab[t][0], b = s_ab[t][1] * s_v[t][warp];
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < DR; ++i) {
-        S[i] = fmaf(a, S[i], b * cur[u].k[i]);
-        dot = fmaf(S[i], cur[u].q[i] * qs, dot);
+        S[i] = fmaf(a, S[i], b * s_qk[t][1][lane + 32 * i]);
+        dot = fmaf(S[i], s_qk[t][0][lane + 32 * i], dot);
       }
       dot = warp_sum(dot);
-      m = cur[u].m;
+      m = s_ab[t][2];
       if (lane == 0) {
-        float* orow = p.o + ((int64_t)(r0 + g0 + u) * H + hd) * (dv + 2);
+        float* orow = p.o + ((int64_t)(r0 + c0 + t) * H + hd) * (dv + 2);
         orow[j] = dot;
         if (j == dv) orow[dv + 1] = m;
       }
     }
   }
+  if (!live) return;
 #pragma unroll
   for (int i = 0; i < DR; ++i) {
     const int d = lane + 32 * i;
@@ -731,6 +804,27 @@ int launch_stack_norm_add(float* x, const void* y, bool y_bf16, const float* w, 
   return B200_OK;
 }
 
+int launch_stack_norm_add_norm(float* x, const void* y, bool y_bf16, const float* w_post, void* h, const float* w_next,
+                               int64_t rows, int dim, float eps, float offset, float mult, int kind, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(x && y && w_post && h && w_next && rows > 0 && dim > 0, "stack norm_add_norm: bad arguments");
+  if (kind != B200_NORM_LAYER || dim > 256 * kLn2Regs) {   // two launches do the same
+    int rc = launch_stack_norm_add(x, y, y_bf16, w_post, rows, dim, eps, mult, kind, st);
+    if (rc != B200_OK) return rc;
+    return launch_stack_norm(h, x, w_next, nullptr, rows, dim, eps, offset, kind, dtype, st);
+  }
+  const dim3 grid((unsigned)rows);
+#define B200_LN2(YT, HT)                                                                                                     \
+  B200_CUDA(launch_pdl(stack_layernorm2_kernel<YT, HT>, grid, dim3(256), 0, st, stack_pdl(), x, (const YT*)y, w_post, (HT*)h, \
+                       w_next, dim, eps, offset, mult))
+  if (y_bf16 && dtype == B200_F32) B200_LN2(__nv_bfloat16, float);
+  else if (y_bf16) B200_LN2(__nv_bfloat16, __nv_bfloat16);
+  else if (dtype == B200_F32) B200_LN2(float, float);
+  else B200_LN2(float, __nv_bfloat16);
+#undef B200_LN2
+  return B200_OK;
+}
+
 int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu, int64_t rows, int n, float limit, int dtype,
                            cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
@@ -838,7 +932,7 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
     LatentRun q = p;
     const size_t al = dtype == B200_F32 ? 32 : 16;
     q.stage_vec = ((size_t)kd * esz) % al == 0 && (reinterpret_cast<uintptr_t>(p.cache) % al) == 0 &&
-                  ((size_t)p.slot_stride * esz) % al == 0 && (32 * kd) % 8 == 0;
+                  ((size_t)p.slot_stride * esz) % al == 0 && (reinterpret_cast<uintptr_t>(p.qa) % al) == 0;
     if (dtype == B200_F32) {
       B200_CUDA(launch_pdl(latent_attn_split_kernel<float>, grid, dim3(256), split_smem, st, stack_pdl(), q));
       B200_CUDA(launch_pdl(latent_merge_kernel<float>, dim3(p.n_tok, H), dim3(256), 0, st, stack_pdl(), q));

@@ -12,6 +12,10 @@ int launch_stack_norm(void* y, const float* x, const float* w, const int32_t* ro
 // x[r, :] += mult · norm(y[r, :]) · w, y fp32 or bf16
 int launch_stack_norm_add(float* x, const void* y, bool y_bf16, const float* w, int64_t rows, int dim, float eps, float mult,
                           int kind, cudaStream_t st);
+// x[r, :] += mult · norm(y[r, :]) · w_post, then h[r, :] = T(norm(x[r, :]) · (offset + w_next)): a sublayer's post-norm, the
+// residual sum and the next sublayer's pre-norm in one pass (layer norms of rows up to 8192 wide; else two launches)
+int launch_stack_norm_add_norm(float* x, const void* y, bool y_bf16, const float* w_post, void* h, const float* w_next,
+                               int64_t rows, int dim, float eps, float offset, float mult, int kind, int dtype, cudaStream_t st);
 // y[r, j] = T(min(g, limit)·sigmoid(1.702·min(g, limit))·(clamp(u, ±limit) + 1)), g = gu[r, j], u = gu[r, n + j]
 int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu, int64_t rows, int n, float limit, int dtype,
                            cudaStream_t st);
