@@ -352,14 +352,18 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
 // ------------------------------------------------------------------------------------- latent attention, decode-shaped
 // One CTA of eight warps per (row, split of the key list).  The split's key rows [c | rotated key part] are staged in
 // shared memory 32 at a time and serve ALL heads (warp w takes heads w, w + 8, …): the rows are read from memory once per
-// row of the step instead of once per head.  Per head and chunk: 32 scores (every key's dot product by the whole warp),
-// the online softmax, the weighted latents.  Partials go to split_ws; latent_merge_kernel joins the splits.
+// row of the step instead of once per head.  Scores: warp w keeps keys 4w … 4w+3 of the chunk in registers, every head's
+// query streams past them from shared memory and the four dot products are summed over the warp side by side; the
+// chunk's scores [head][key] go through shared memory to the heads' warps.  Then per head: the online softmax and the
+// weighted latents.  Partials go to split_ws; latent_merge_kernel joins the splits.
 constexpr int kLatHeadsPerWarp = 4;   // heads <= 32
+constexpr int kLatKeyRegs = 20;       // cache row (kv_rank + rot_dim) <= 640
 template <typename T>
 __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun p) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float sm[];
+  __shared__ float sc[8 * kLatHeadsPerWarp * 32];   // the chunk's scores [head][key]
   const int t = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = p.l.kv_rank, kd = r + p.l.rot_dim, H = p.a.heads;
   float* q = sm;                          // [H][kd], scaled
@@ -405,19 +409,38 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
       }
     }
     __syncthreads();
+    {   // scores: warp w holds keys 4w … 4w+3 of the chunk in registers and lets every head's query stream past them
+      float kreg[4][kLatKeyRegs];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int ii = 0; ii < kLatKeyRegs; ++ii) {
+          const int c = lane + 32 * ii;
+          kreg[u][ii] = (4 * warp + u < cnt && c < kd) ? kc[(size_t)(4 * warp + u) * kd + c] : 0.f;
+        }
+      for (int hd = 0; hd < H; ++hd) {
+        const float* qh = q + (size_t)hd * kd;
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ii = 0; ii < kLatKeyRegs; ++ii) {
+          const int c = lane + 32 * ii;
+          const float qv = c < kd ? qh[c] : 0.f;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) d[u] = fmaf(qv, kreg[u][ii], d[u]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+          for (int u = 0; u < 4; ++u) d[u] += __shfl_xor_sync(0xffffffffu, d[u], o);
+        if (lane < 4) sc[hd * 32 + 4 * warp + lane] = lane == 0 ? d[0] : lane == 1 ? d[1] : lane == 2 ? d[2] : d[3];
+      }
+    }
+    __syncthreads();
 #pragma unroll
     for (int u = 0; u < kLatHeadsPerWarp; ++u) {
       const int hd = warp + 8 * u;
       if (hd >= H) break;
-      const float* qh = q + (size_t)hd * kd;
-      float s_mine = -INFINITY;
-      for (int jj = 0; jj < cnt; ++jj) {
-        const float* kr = kc + (size_t)jj * kd;
-        float d = 0.f;
-        for (int i = lane; i < kd; i += 32) d = fmaf(qh[i], kr[i], d);
-        d = warp_sum(d);
-        if (lane == jj) s_mine = d;
-      }
+      const float s_mine = lane < cnt ? sc[hd * 32 + lane] : -INFINITY;
       const float m_new = fmaxf(m[u], warp_max(s_mine));
       const float pr = lane < cnt ? expf(s_mine - m_new) : 0.f;
       const float corr = expf(m[u] - m_new);
@@ -527,8 +550,10 @@ __global__ void __launch_bounds__(32) mlstm_gates_kernel(const MlstmRun p) {
     }
     float before = 0.f, after = 0.f;
     const int n = min(32, cnt - t0);
-    for (int u = 0; u < n; ++u) {
-      const float m_new = fmaxf(__shfl_sync(0xffffffffu, gf, u) + m_prev, __shfl_sync(0xffffffffu, gi, u));
+#pragma unroll
+    for (int u = 0; u < 32; ++u) {   // fixed length: the 64 shuffles do not wait for the walk
+      const float fu = __shfl_sync(0xffffffffu, gf, u), iu = __shfl_sync(0xffffffffu, gi, u);
+      const float m_new = u < n ? fmaxf(fu + m_prev, iu) : m_prev;
       if (lane == u) {
         before = m_prev;
         after = m_new;
@@ -607,20 +632,31 @@ __global__ void __launch_bounds__(256) mlstm_scan_kernel(const MlstmRun p) {
     if (c0 + CH < cnt) fetch(c0 + CH);
     if (!live) continue;
     const int n = min(CH, cnt - c0);
-    for (int t = 0; t < n; ++t) {
-      const float a = s_ab[t][0], b = s_ab[t][1] * s_v[t][warp];
-      float dot = 0.f;
+    for (int t4 = 0; t4 < n; t4 += 4) {   // four tokens' dots are summed over the warp side by side
+      float dot[4];
 #pragma unroll
-      for (int i = 0; i < DR; ++i) {
-        S[i] = fmaf(a, S[i], b * s_qk[t][1][lane + 32 * i]);
-        dot = fmaf(S[i], s_qk[t][0][lane + 32 * i], dot);
+      for (int u = 0; u < 4; ++u) {
+        const int t = t4 + u;             // t < CH always (CH is a multiple of 4); rows past n hold zeros with a = b = 0
+        const bool on = t < n;
+        const float a = on ? s_ab[t][0] : 1.f, b = on ? s_ab[t][1] * s_v[t][warp] : 0.f;
+        dot[u] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DR; ++i) {
+          S[i] = fmaf(a, S[i], b * s_qk[t][1][lane + 32 * i]);
+          dot[u] = fmaf(S[i], s_qk[t][0][lane + 32 * i], dot[u]);
+        }
+        if (on) m = s_ab[t][2];
       }
-      dot = warp_sum(dot);
-      m = s_ab[t][2];
-      if (lane == 0) {
-        float* orow = p.o + ((int64_t)(r0 + c0 + t) * H + hd) * (dv + 2);
-        orow[j] = dot;
-        if (j == dv) orow[dv + 1] = m;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+      }
+      if (lane < 4 && t4 + lane < n) {
+        float* orow = p.o + ((int64_t)(r0 + c0 + t4 + lane) * H + hd) * (dv + 2);
+        const float mine = lane == 0 ? dot[0] : lane == 1 ? dot[1] : lane == 2 ? dot[2] : dot[3];
+        orow[j] = mine;
+        if (j == dv) orow[dv + 1] = s_ab[t4 + lane][2];
       }
     }
   }
@@ -921,7 +957,8 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
     if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
   }
   const size_t split_smem = (size_t)(H + 32) * kd * 4;
-  if (small && p.split_ws != nullptr && p.nsplit >= 1 && H <= 8 * kLatHeadsPerWarp && split_smem <= 200 * 1024) {
+  if (small && p.split_ws != nullptr && p.nsplit >= 1 && H <= 8 * kLatHeadsPerWarp && kd <= 32 * kLatKeyRegs &&
+      split_smem <= 200 * 1024) {
     static bool attr_done = false;
     if (!attr_done) {
       B200_CUDA(cudaFuncSetAttribute(latent_attn_split_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
