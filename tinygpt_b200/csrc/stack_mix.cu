@@ -781,26 +781,25 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const MoeRun p) {
   for (int i = threadIdx.x; i < p.width; i += blockDim.x) dst[i] = cvt<T>(w * ldf<T>(src + i));
 }
 
-// y[t, :] = Σ_k outp[slot of (t, k), :] + sigmoid(sg[t]) · shared[t, :]
+// y[t, :] = Σ_k outp[slot of (t, k), :] + sigmoid(sg[t]) · shared[t, :]   — one thread per (token, column)
 template <typename T>
-__global__ void __launch_bounds__(128) moe_combine_kernel(const MoeRun p) {
+__global__ void __launch_bounds__(256) moe_combine_kernel(const MoeRun p) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, top = p.m.top;
-  float gate = 0.f;
-  if (p.shared != nullptr) gate = 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
-  for (int i = threadIdx.x; i < p.width; i += blockDim.x) {
-    float v = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const int64_t o = (int64_t)p.pair_slot[(int64_t)t * top + k] * p.width + i;
-      v += p.tc ? __bfloat162float(p.outp_bf[o]) : p.outp[o];
-    }
-    if (p.shared != nullptr) {
-      const int64_t o = (int64_t)t * p.width + i;
-      v += gate * (p.shared_f32 ? static_cast<const float*>(p.shared)[o] : ldf<T>(static_cast<const T*>(p.shared) + o));
-    }
-    p.y[(int64_t)t * p.width + i] = v;
+  const int t = blockIdx.x, top = p.m.top, i = blockIdx.y * 256 + threadIdx.x;
+  if (i >= p.width) return;
+  const int32_t* slots = p.pair_slot + (int64_t)t * top;
+  float v = 0.f;
+  for (int k = 0; k < top; ++k) {
+    const int64_t o = (int64_t)slots[k] * p.width + i;
+    v += p.tc ? __bfloat162float(p.outp_bf[o]) : p.outp[o];
   }
+  if (p.shared != nullptr) {
+    const float gate = 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
+    const int64_t o = (int64_t)t * p.width + i;
+    v += gate * (p.shared_f32 ? static_cast<const float*>(p.shared)[o] : ldf<T>(static_cast<const T*>(p.shared) + o));
+  }
+  p.y[(int64_t)t * p.width + i] = v;
 }
 
 }  // namespace
@@ -1131,8 +1130,9 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   if ((rc = launch_stack_gemm(d, dtype, st)) != B200_OK) return rc;
   }
   }
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_combine_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
-  else B200_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
+  const dim3 cg(p.n_tok, (p.width + 255) / 256);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_combine_kernel<float>, cg, dim3(256), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(moe_combine_kernel<__nv_bfloat16>, cg, dim3(256), 0, st, stack_pdl(), p));
   return B200_OK;
 }
 
