@@ -70,10 +70,11 @@ def latent_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mixer:
     H, dn, dr, dv, r = mixer["heads"], mixer["dim"], mixer["rot_dim"], mixer["vdim"], mixer["kv_rank"]
     pos = torch.arange(T) if positions is None else positions
     q = (h @ w[p + "q"].T).view(T, H, dn + dr)
-    q_plain, q_rot = q[..., :dn], rotate(q[..., dn:], pos, mixer["rot"])
     down = h @ w[p + "dkv"].T
     c = unit_rms(down[:, :r], eps) * w[p + "dkv.norm"]
-    k_rot = rotate(down[:, r:], pos, mixer["rot"])                                # [T, dr], shared by the heads
+    q_plain, q_rot, k_rot = q[..., :dn], q[..., dn:], down[:, r:]                 # k_rot [T, dr] is shared by the heads
+    if mixer.get("rot"):
+        q_rot, k_rot = rotate(q_rot, pos, mixer["rot"]), rotate(k_rot, pos, mixer["rot"])
     k_plain = (c @ w[p + "uk"].T).view(T, H, dn)
     v = (c @ w[p + "uv"].T).view(T, H, dv)
     out = torch.zeros(T, H, dv, dtype=h.dtype)

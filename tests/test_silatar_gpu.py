@@ -45,9 +45,11 @@ ROT = {"base": 10000.0, "dims": 8, "scaling": {"factor": 8.0, "fast": 16.0, "ori
 
 
 def latent(heads=3, dim=12, rot_dim=8, vdim=20, kv_rank=40, rot=None):
-    return {"type": "latent_attention",
-            "mixer": {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
-                      "scale": 1.0 / math.sqrt(dim + rot_dim), "rot": dict(rot or ROT)}}
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank,
+         "scale": 1.0 / math.sqrt(dim + rot_dim)}
+    if rot_dim > 0:
+        m["rot"] = dict(rot or ROT)
+    return {"type": "latent_attention", "mixer": m}
 
 
 def mlstm(heads=3, dim=16, vdim=24, cap=12.0):
@@ -346,7 +348,7 @@ def test_slot_given_back_and_used_again(dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("case", ["no_loop", "loop_all", "loop_tail", "no_mlp", "top1_no_shared", "odd_sizes", "one_head",
-                                  "plain_rotary"])
+                                  "plain_rotary", "wide_latent", "no_rotary"])
 def test_other_orders_and_sizes(dtype, case):
     if case == "no_loop":
         cfg = config([(mlstm(), moe()), (latent(), dense())])
@@ -365,6 +367,11 @@ def test_other_orders_and_sizes(dtype, case):
     elif case == "one_head":
         cfg = config([(latent(heads=1, dim=32, rot_dim=16, vdim=48, kv_rank=64, rot=dict(ROT, dims=16)), dense(64)),
                       (mlstm(heads=1, dim=64, vdim=32), dense(32))], width=128)
+    elif case == "wide_latent":      # a latent wider than the split-key decode kernel takes
+        cfg = config([(latent(heads=2, dim=8, rot_dim=4, vdim=8, kv_rank=544, rot={"base": 100.0, "dims": 4}), dense(32)),
+                      (mlstm(heads=1, dim=8, vdim=8), None)])
+    elif case == "no_rotary":        # no rotated part at all
+        cfg = config([(latent(heads=2, dim=16, rot_dim=0, vdim=8, kv_rank=24), dense(32)), (mlstm(), dense())])
     else:
         cfg = config([(latent(rot={"base": 1000.0, "dims": 8}), dense()), (mlstm(), dense())])
     eng, w = make(cfg, dtype, seed=3)

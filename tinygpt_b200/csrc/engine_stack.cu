@@ -210,7 +210,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_ms = take(s->any_moe ? P * 4 : 0), o_ma = take(s->any_moe ? P * W * s->esz : 0);
   const size_t o_mg = take(s->any_moe ? P * 2 * s->moe_ff_max * s->esz : 0), o_mc = take(s->any_moe ? P * s->moe_ff_max * s->esz : 0);
   const size_t o_mo = take(s->any_moe ? P * W * 4 : 0), o_mb = take(s->any_moe && s->fast ? P * W * 2 : 0);
-  const size_t o_lw = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * s->lat_heads_max * kLatentMaxSplits * (2 + s->lat_rank_max) * 4 : 0);
+  const size_t o_lw = take(s->lat_rank_max > 0 ? (size_t)kSmallRows * s->lat_heads_max * kLatentMaxSplits * (2 + std::min(s->lat_rank_max, 512)) * 4 : 0);
   const bool lx = s->fast && s->lat_rank_max > 0;
   const size_t C = d.max_ctx;
   const size_t o_lc = take(lx ? C * s->lat_rank_max * 2 : 0), o_lkp = take(lx ? C * s->lat_hd_max * 2 : 0);

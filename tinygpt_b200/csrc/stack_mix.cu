@@ -194,8 +194,8 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const LatentRun p) {
 // [c_j | rotated key part], value j is c_j — the same row.  A warp walks keys 32 at a time: every key's dot product is
 // taken by the whole warp over the row's columns, lane l keeps the score of key l, the chunk joins an online softmax and
 // the rows are read once more as values.  The warps' partial softmaxes meet in shared memory.
-constexpr int kLatVR = kLatentMaxRank / 32;
-template <typename T>
+constexpr int kLatVR = 16;   // latents up to 512 entries in the split-key kernel and the common case of this one
+template <typename T, int VR>
 __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
   pdl_trigger();
   pdl_wait();
@@ -209,9 +209,9 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
   __syncthreads();
   const int n_keys = p.pos[t] + 1;
   const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
-  float m = -INFINITY, sum = 0.f, acc[kLatVR];
+  float m = -INFINITY, sum = 0.f, acc[VR];
 #pragma unroll
-  for (int i = 0; i < kLatVR; ++i) acc[i] = 0.f;
+  for (int i = 0; i < VR; ++i) acc[i] = 0.f;
   for (int j0 = warp * 32; j0 < n_keys; j0 += 128) {
     const int cnt = min(32, n_keys - j0);
     float s_mine = -INFINITY;
@@ -227,12 +227,12 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
     const float corr = expf(m - m_new);   // m = −inf on the first chunk: 0
     sum = sum * corr + warp_sum(pr);
 #pragma unroll
-    for (int i = 0; i < kLatVR; ++i) acc[i] *= corr;
+    for (int i = 0; i < VR; ++i) acc[i] *= corr;
     for (int jj = 0; jj < cnt; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, pr, jj);
       const T* kr = K + (int64_t)(j0 + jj) * kd;
 #pragma unroll
-      for (int i = 0; i < kLatVR; ++i)
+      for (int i = 0; i < VR; ++i)
         if (lane + 32 * i < r) acc[i] = fmaf(pj, ldf<T>(kr + lane + 32 * i), acc[i]);
     }
     m = m_new;
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
     mine[1] = sum;
   }
 #pragma unroll
-  for (int i = 0; i < kLatVR; ++i)
+  for (int i = 0; i < VR; ++i)
     if (lane + 32 * i < r) mine[2 + lane + 32 * i] = acc[i];
   __syncthreads();
   float M = -INFINITY;
@@ -956,7 +956,7 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
     if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
   }
   const size_t split_smem = (size_t)(H + 32) * kd * 4;
-  if (small && p.split_ws != nullptr && p.nsplit >= 1 && H <= 8 * kLatHeadsPerWarp && kd <= 32 * kLatKeyRegs &&
+  if (small && p.split_ws != nullptr && p.nsplit >= 1 && H <= 8 * kLatHeadsPerWarp && kd <= 32 * kLatKeyRegs && r <= 32 * kLatVR &&
       split_smem <= 200 * 1024) {
     static bool attr_done = false;
     if (!attr_done) {
@@ -978,8 +978,15 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
     }
   } else {
     const size_t smem = (size_t)(kd + 4 * (2 + r)) * 4;
-    if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
-    else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16>, dim3(p.n_tok, H), dim3(128), smem, st, stack_pdl(), p));
+    const dim3 grid(p.n_tok, H);
+    if (r <= 32 * kLatVR) {
+      if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float, kLatVR>, grid, dim3(128), smem, st, stack_pdl(), p));
+      else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16, kLatVR>, grid, dim3(128), smem, st, stack_pdl(), p));
+    } else {
+      constexpr int kWide = kLatentMaxRank / 32;
+      if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_attn_kernel<float, kWide>, grid, dim3(128), smem, st, stack_pdl(), p));
+      else B200_CUDA(launch_pdl(latent_attn_kernel<__nv_bfloat16, kWide>, grid, dim3(128), smem, st, stack_pdl(), p));
+    }
   }
   // head h's output = uv_h · (softmax-weighted latent of head h)
   if (small) {

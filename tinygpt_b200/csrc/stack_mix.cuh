@@ -50,7 +50,7 @@ int launch_skinny_f32(float* C, const void* A, const void* W, const float* bias_
                       cudaStream_t st);
 
 // ---- latent attention: everything between the in-projection and the out-projection
-constexpr int kLatentMaxRank = 512;
+constexpr int kLatentMaxRank = 1024;
 struct LatentRun {
   b200_attn_desc a{};
   b200_latent_desc l{};

@@ -216,7 +216,7 @@ class RotarySpec:
     def frequencies(self) -> Tuple[np.ndarray, float]:
         """→ (angular frequency per pair [dims/2] in float64, magnitude of cos / sin)."""
         i = np.arange(self.dims // 2, dtype=np.float64)
-        f = np.power(float(self.base), -2.0 * i / self.dims)
+        f = np.power(float(self.base), -2.0 * i / max(self.dims, 1))
         if self.factor <= 0:
             return f, 1.0
 
@@ -447,7 +447,7 @@ def silatar_from_config(doc: dict, name: str = "Silatar") -> StackSpec:
         kind, m = lc.get("type"), lc["mixer"]
         kw = {}
         if kind == "latent_attention":
-            rot = _rotary_from_config(m["rot"])
+            rot = _rotary_from_config(m["rot"]) if m.get("rot") else RotarySpec(dims=0, base=10000.0)
             if rot.dims % 2 or rot.dims > int(m["rot_dim"]):
                 raise ValueError(f"Silatar: layer {i}: rot.dims {rot.dims} must be even and at most rot_dim")
             kw = dict(mixer=kind, latent=LatentSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]),
@@ -479,7 +479,7 @@ def silatar_from_config(doc: dict, name: str = "Silatar") -> StackSpec:
                      loop_times=int(loop.get("times", 0)), norm_eps=float(doc["norm"]["eps"]), norm_offset=0.0,
                      block="sandwich", norm_kind="layer", loop_mix=False,
                      logit_softcap=float(doc.get("logit_softcap") or 0.0))
-    if spec.loop_times > 0 and not 0 <= spec.loop_start < spec.loop_stop <= len(layers):
+    if spec.loop_times > 0 and not 0 <= spec.loop_start <= spec.loop_stop <= len(layers):
         raise ValueError(f"Silatar: loop {spec.loop_start}..{spec.loop_stop} does not fit {len(layers)} layers")
     return spec
 
