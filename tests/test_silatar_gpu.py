@@ -382,6 +382,25 @@ def test_other_orders_and_sizes(dtype, case):
     assert_close(torch.cat(rows), want, dtype, case)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_expert_layers_of_unequal_count_share_the_engine(dtype):
+    """Eight experts in one layer, three in the next, and prompt after prompt through the same engine: what one layer's
+    routing leaves behind must not reach the other's.  Every prompt must come out as from an engine that has seen nothing
+    before (both number formats), and as the restatement has it (fp32)."""
+    cfg = config([(latent(), moe(experts=8, top=2, ff=16, shared=None)), (mlstm(), moe(experts=3, top=2, ff=24))], loop=(0, 2, 2))
+    eng, w = make(cfg, dtype, seed=5)
+    for seed, n in ((1, 60), (2, 24), (3, 41), (4, 12)):
+        toks = tokens(n, cfg["vocab"], seed)
+        got = eng.step([(0, toks, list(range(n)))])
+        eng.release(0)
+        fresh, _ = make(cfg, dtype, seed=5)
+        alone = fresh.step([(0, toks, list(range(n)))])
+        fresh.close()
+        assert float(row_err(got, alone).max()) < 1e-5, f"prompt of {n} after others"
+        if dtype == torch.float32:
+            assert_close(got, so.forward(cfg, w, toks), dtype, f"prompt of {n}")
+
+
 def test_the_constants_matter():
     """Moving one constant of the design moves the logits: none of them is ignored on the way to the engine."""
     cfg = base_config()

@@ -668,6 +668,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   MoeRun m = s->moe_ws;
   m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
   m.small = n_tok <= kSmallRows;
+  m.plan_stride = s->moe_e_max;
   m.tc = s->fast && n_tok >= kGemmRows && gemm_shape_ok(2 * L.moe.expert_ff, W) && gemm_shape_ok(W, L.moe.expert_ff);
   if (m.tc) {   // that path reads the group sizes back: not inside a stream capture
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;

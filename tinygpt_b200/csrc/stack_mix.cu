@@ -744,9 +744,10 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(const MoeRun p) {
   pdl_wait();
   extern __shared__ int sh[];   // cursor [E]
   const int E = p.m.experts, P = p.n_tok * p.m.top, n_tiles = moe_tiles(P, E);
+  const int S = p.plan_stride > 0 ? p.plan_stride : E;
   int32_t* counts = p.plan;
-  int32_t* group_end = p.plan + E;
-  int32_t* tile_group = p.plan + 2 * E;
+  int32_t* group_end = p.plan + S;
+  int32_t* tile_group = p.plan + 2 * S;
   int32_t* tile_row0 = tile_group + n_tiles;
   if (threadIdx.x == 0) {
     int row = 0, tile = 0;
@@ -1041,7 +1042,8 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(m.experts > 0 && m.top > 0 && m.top <= m.experts && m.expert_ff > 0 && m.router && m.w_exp_in && m.w_exp_out,
                  "moe: bad description");
   B200_CHECK_ARG(m.experts <= 8192, "moe: more than 8192 experts not built");
-  const int P = p.n_tok * m.top, n_tiles = moe_tiles(P, m.experts), E = m.experts;
+  const int P = p.n_tok * m.top, n_tiles = moe_tiles(P, m.experts), E = m.experts, S = p.plan_stride > 0 ? p.plan_stride : E;
+  B200_CHECK_ARG(S >= E, "moe: plan stride below the expert count");
   int rc;
   if (p.small) {   // a few tokens: router, then every (token, choice) pair is an item of a small product with its expert
     B200_CHECK_ARG(p.n_tok <= kSmallRows, "moe: the small path takes up to %d tokens", kSmallRows);
@@ -1072,7 +1074,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   if (p.tc) {
     B200_CHECK_ARG(dtype == B200_BF16 && p.outp_bf != nullptr, "moe: the tensor-core path is bf16");
     std::vector<int32_t> ends(E);
-    B200_CUDA(cudaMemcpyAsync(ends.data(), p.plan + E, (size_t)E * 4, cudaMemcpyDeviceToHost, st));
+    B200_CUDA(cudaMemcpyAsync(ends.data(), p.plan + S, (size_t)E * 4, cudaMemcpyDeviceToHost, st));
     B200_CUDA(cudaStreamSynchronize(st));
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.a_perm;
     __nv_bfloat16 *GU = (__nv_bfloat16*)p.gu, *ACT = (__nv_bfloat16*)p.act;
@@ -1124,7 +1126,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width;
   g.M = P; g.N = 2 * m.expert_ff; g.K = p.width;
   g.epi = SEPI_STORE; g.c = p.gu; g.ldc = 2 * m.expert_ff;
-  g.tile_group = p.plan + 2 * E; g.tile_row0 = p.plan + 2 * E + n_tiles; g.group_end = p.plan + E; g.n_tiles = n_tiles;
+  g.tile_group = p.plan + 2 * S; g.tile_row0 = p.plan + 2 * S + n_tiles; g.group_end = p.plan + S; g.n_tiles = n_tiles;
   if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
   if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, 2 * m.expert_ff, P, m.expert_ff, m.limit, dtype, st)) != B200_OK)
     return rc;

@@ -133,7 +133,9 @@ struct MoeRun {
   float* z = nullptr;            // [n_tok, experts] router logits
   int32_t* sel_e = nullptr;      // [n_tok·top] chosen expert of every (token, choice) pair
   float* sel_w = nullptr;        // [n_tok·top] its score
-  int32_t* plan = nullptr;       // counts [E] | group_end [E] | tile_group [n_tiles] | tile_row0 [n_tiles]
+  int32_t* plan = nullptr;       // counts [S] | group_end [S] | tile_group [n_tiles] | tile_row0 [n_tiles], S = plan_stride
+  int plan_stride = 0;           // >= experts; 0: experts.  Layers of unequal expert counts share one plan: the counts (kept
+                                 // zero between uses) of one must not lie under the other arrays of another
   int32_t* pair_slot = nullptr;  // [n_tok·top] sorted position of a pair
   void* a_perm = nullptr;        // [P, width] T: score·h of every pair, sorted by expert
   void* gu = nullptr;            // [P, 2·expert_ff] T
@@ -153,7 +155,7 @@ struct MoeRun {
   __nv_bfloat16* outp_bf = nullptr;   // [P, width]
 };
 __host__ __device__ inline int moe_tiles(int pairs, int experts) { return (pairs + 63) / 64 + experts; }
-inline int64_t moe_plan_ints(int pairs, int experts) { return 2 * (int64_t)experts + 2 * moe_tiles(pairs, experts); }
+inline int64_t moe_plan_ints(int pairs, int experts) { return 2 * (int64_t)experts + 2 * moe_tiles(pairs, experts); }   // experts = the stride
 int run_moe(const MoeRun& p, int dtype, cudaStream_t st);
 
 }  // namespace b200
