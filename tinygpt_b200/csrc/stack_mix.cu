@@ -1079,9 +1079,9 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.a_perm;
     __nv_bfloat16 *GU = (__nv_bfloat16*)p.gu, *ACT = (__nv_bfloat16*)p.act;
     const int64_t f2 = 2ll * m.expert_ff;
-    // one expert's rows rarely fill the GPU: the experts' products go round four side streams that fork from and join
+    // one expert's rows rarely fill the GPU: the experts' products go round eight side streams that fork from and join
     // back into the step's stream
-    constexpr int kSide = 4;
+    constexpr int kSide = 8;
     static cudaStream_t side[kSide];
     static cudaEvent_t fork_ev, join_ev[kSide];
     static bool side_ok = false;
